@@ -1,1 +1,1 @@
-from . import llama, ravapel, rugedra  # noqa: F401 (register LlamaForCausalLM, Ravapel and Rugedra)
+from . import llama, ravapel, rugedra, vofanex  # noqa: F401 (register LlamaForCausalLM, Ravapel, Rugedra and Vofanex)

@@ -17,6 +17,9 @@
 // `chunk` > 0: a query sees only the keys of its own chunk of that many positions (counted from the
 // request's position 0).  `head_bias` != null: the weight of a visible key is sigmoid(score +
 // head_bias[head]) and the weights are not normalised over the keys (no softmax).
+// `sinks` != null (softmax only): the denominator holds one more term exp(sinks[head]) that has no
+// key and no value; it is the state the running maximum and sum start from.  `out_gate` != null:
+// the head's result is multiplied by sigmoid(out_gate[token * gate_ld + head]).
 #include "common.cuh"
 #include <math.h>
 
@@ -62,6 +65,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                const int* __restrict__ positions, T* __restrict__ out,
                                int nh, int nkv, int hd, int hdv, int v_stride, int page_size, int total_pages,
                                float scale, int window, int chunk, const float* __restrict__ head_bias,
+                               const float* __restrict__ sinks, const float* __restrict__ out_gate, int gate_ld,
                                int* err) {
     extern __shared__ float q_smem[];  // [WARPS][hd]
     ie_pdl_trigger();
@@ -83,6 +87,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
     const bool gated = head_bias != nullptr;  // sigmoid(score + bias) per key, not normalised over keys
     float hb = gated ? head_bias[head] : 0.f;
     float m = -INFINITY, l = 0.f;
+    if (!gated && sinks != nullptr) { m = sinks[head]; l = 1.0f; }
     float acc[MAX_ACC];
 #pragma unroll
     for (int i = 0; i < MAX_ACC; ++i) acc[i] = 0.f;
@@ -130,6 +135,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
     }
     T* orow = out + ((size_t)token * nh + head) * hdv;
     float inv = gated ? 1.0f : (l > 0.f ? 1.0f / l : 0.f);
+    if (out_gate != nullptr) inv *= 1.0f / (1.0f + expf(-out_gate[(size_t)token * gate_ld + head]));
 #pragma unroll
     for (int i = 0; i < MAX_ACC; ++i) {
         int d = lane + 32 * i;
@@ -143,7 +149,8 @@ IE_API int ie_paged_attention_generic(const void* q, const void* k_cache, const 
                                       const int* seq_of_token, const int* positions, void* out,
                                       int num_tokens, int nh, int nkv, int hd, int hdv, int v_stride,
                                       int page_size, int total_pages, float scale, int window, int chunk,
-                                      const float* head_bias, int* err, void* stream) {
+                                      const float* head_bias, const float* sinks, const float* out_gate,
+                                      int gate_ld, int* err, void* stream) {
     if (num_tokens <= 0) return 0;
     if (hd < 1 || hdv < 1 || hdv > 32 * MAX_ACC || nkv <= 0 || nh % nkv != 0) return (int)cudaErrorInvalidValue;
     dim3 grid((nh + WARPS - 1) / WARPS, num_tokens);
@@ -153,11 +160,11 @@ IE_API int ie_paged_attention_generic(const void* q, const void* k_cache, const 
         paged_attention_generic_kernel<<<grid, WARPS * 32, smem, s>>>(
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
             block_tables, table_width, seq_of_token, positions, (__nv_bfloat16*)out,
-            nh, nkv, hd, hdv, v_stride, page_size, total_pages, scale, window, chunk, head_bias, err);
+            nh, nkv, hd, hdv, v_stride, page_size, total_pages, scale, window, chunk, head_bias, sinks, out_gate, gate_ld, err);
     else
         paged_attention_generic_kernel<<<grid, WARPS * 32, smem, s>>>(
             (const float*)q, (const float*)k_cache, (const float*)v_cache,
             block_tables, table_width, seq_of_token, positions, (float*)out,
-            nh, nkv, hd, hdv, v_stride, page_size, total_pages, scale, window, chunk, head_bias, err);
+            nh, nkv, hd, hdv, v_stride, page_size, total_pages, scale, window, chunk, head_bias, sinks, out_gate, gate_ld, err);
     return IE_LAUNCH_CHECK();
 }

@@ -4,11 +4,12 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------------------------
-// Embedding: out[n, :] = float(table[ids[n], :])          (engine/model/llama.py:25,61)
+// Embedding: out[n, :] = float(table[ids[n], :]) * scale   (engine/model/llama.py:25,61; a model
+// that multiplies its embedding by a constant passes it as `scale`, 1 otherwise)
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                 float* __restrict__ out, int hidden, int vocab, int* err) {
+                                 float* __restrict__ out, int hidden, int vocab, float scale, int* err) {
     ie_pdl_trigger();
     ie_pdl_wait();
     int row = blockIdx.x;
@@ -17,19 +18,19 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
     if (!ok && threadIdx.x == 0) ie_report(err, IE_ERR_TOKEN_ID, id, row);
     const T* src = table + (size_t)(ok ? id : 0) * hidden;
     float* dst = out + (size_t)row * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? ie_load(src + i) : 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? ie_load(src + i) * scale : 0.f;
 }
 
 IE_API int ie_embedding(const void* table, int table_dtype, const int* ids, float* out,
-                        int num_tokens, int hidden, int vocab, int* err, void* stream) {
+                        int num_tokens, int hidden, int vocab, float scale, int* err, void* stream) {
     if (num_tokens <= 0) return 0;
     int threads = hidden >= 1024 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
     if (table_dtype == IE_BF16)
         return ie_launch(embedding_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, s,
-                         (const __nv_bfloat16*)table, ids, out, hidden, vocab, err);
+                         (const __nv_bfloat16*)table, ids, out, hidden, vocab, scale, err);
     return ie_launch(embedding_kernel<float>, dim3(num_tokens), dim3(threads), 0, s, (const float*)table, ids,
-                     out, hidden, vocab, err);
+                     out, hidden, vocab, scale, err);
 }
 
 // ---------------------------------------------------------------------------------------------

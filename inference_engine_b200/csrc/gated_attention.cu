@@ -1,5 +1,8 @@
 // Input stage of an attention whose queries and keys are normalised per head before the rotation,
-// and whose value rows may have another size than its key rows.
+// and whose value rows may have another size than its key rows.  Variants by parameters: a bias on
+// the whole projection (`bias`, laid out like a row of it, added first); no norm on queries or keys
+// (their weight is null); value heads divided by their root mean square over `vdim` (eps inside the
+// root, no weight) before they are cached (`value_norm`).
 //
 // qk_norm_rope_write: from the fused 32-bit projection [N, ld] = (heads * dim queries, kv_heads *
 // dim keys, kv_heads * vdim values): every query and key head is divided by its root mean square
@@ -19,6 +22,7 @@ template <typename T>
 __global__ void __launch_bounds__(QW_WARPS * 32)
 qk_norm_rope_write_kernel(const float* __restrict__ proj, int ld, const int* __restrict__ positions,
                           const float* __restrict__ table, int rot_dims, int table_positions,
+                          const float* __restrict__ bias, int value_norm,
                           const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
                           T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                           const int* __restrict__ slot_mapping, int heads, int kv_heads, int dim, int vdim,
@@ -44,21 +48,40 @@ qk_norm_rope_write_kernel(const float* __restrict__ proj, int ld, const int* __r
         int g = (unit - heads) % kv_heads;
         cache_row = ((long long)page * kv_heads + g) * page_size + (slot % page_size);
     }
-    if (unit >= heads + kv_heads) {  // a value head: copied as it is
+    if (unit >= heads + kv_heads) {  // a value head: copied as it is, or divided by its root mean square
         int g = unit - heads - kv_heads;
-        const float* v = src + (size_t)(heads + kv_heads) * dim + (size_t)g * vdim;
-        for (int d = lane; d < vdim; d += 32) ie_store(v_cache + cache_row * vdim + d, v[d]);
+        size_t col = (size_t)(heads + kv_heads) * dim + (size_t)g * vdim;
+        const float* v = src + col;
+        const float* vb = bias != nullptr ? bias + col : nullptr;
+        float inv = 1.0f;
+        if (value_norm) {
+            float ss = 0.f;
+            for (int d = lane; d < vdim; d += 32) {
+                float e = vb != nullptr ? v[d] + vb[d] : v[d];
+                ss = fmaf(e, e, ss);
+            }
+            ss = warp_sum(ss);
+            inv = 1.0f / sqrtf(ss / (float)vdim + eps);
+        }
+        for (int d = lane; d < vdim; d += 32)
+            ie_store(v_cache + cache_row * vdim + d, (vb != nullptr ? v[d] + vb[d] : v[d]) * inv);
         return;
     }
     bool is_q = unit < heads;
     const float* x = src + (size_t)unit * dim;  // (the key heads follow the query heads)
+    const float* xb = bias != nullptr ? bias + (size_t)unit * dim : nullptr;
     const float* weight = is_q ? q_weight : k_weight;
     float* y = rows + warp * dim;
     float ss = 0.f;
-    for (int d = lane; d < dim; d += 32) ss = fmaf(x[d], x[d], ss);
+    for (int d = lane; d < dim; d += 32) {
+        float e = xb != nullptr ? x[d] + xb[d] : x[d];
+        y[d] = e;
+        ss = fmaf(e, e, ss);
+    }
     ss = warp_sum(ss);
     float inv = 1.0f / sqrtf(ss / (float)dim + eps);
-    for (int d = lane; d < dim; d += 32) y[d] = weight != nullptr ? (x[d] * inv) * weight[d] : x[d];
+    if (weight != nullptr)
+        for (int d = lane; d < dim; d += 32) y[d] = (y[d] * inv) * weight[d];
     __syncwarp();
     int pos = positions[n];
     int half = rot_dims / 2;
@@ -82,7 +105,8 @@ qk_norm_rope_write_kernel(const float* __restrict__ proj, int ld, const int* __r
 }  // namespace
 
 IE_API int ie_qk_norm_rope_write(const float* proj, int ld, const int* positions, const float* table, int rot_dims,
-                                 int table_positions, const float* q_weight, const float* k_weight, float eps,
+                                 int table_positions, const float* bias, int value_norm, const float* q_weight,
+                                 const float* k_weight, float eps,
                                  void* q_out, void* k_cache, void* v_cache, int dtype, const int* slot_mapping,
                                  int num_tokens, int heads, int kv_heads, int dim, int vdim, int page_size,
                                  int total_pages, int* err, void* stream) {
@@ -96,10 +120,10 @@ IE_API int ie_qk_norm_rope_write(const float* proj, int ld, const int* positions
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == IE_BF16)
         return ie_launch(qk_norm_rope_write_kernel<__nv_bfloat16>, grid, dim3(QW_WARPS * 32), smem, s, proj, ld,
-                         positions, table, rot_dims, table_positions, q_weight, k_weight, eps, (__nv_bfloat16*)q_out,
+                         positions, table, rot_dims, table_positions, bias, value_norm, q_weight, k_weight, eps, (__nv_bfloat16*)q_out,
                          (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, slot_mapping, heads, kv_heads, dim, vdim,
                          page_size, total_pages, err);
     return ie_launch(qk_norm_rope_write_kernel<float>, grid, dim3(QW_WARPS * 32), smem, s, proj, ld, positions, table,
-                     rot_dims, table_positions, q_weight, k_weight, eps, (float*)q_out, (float*)k_cache,
+                     rot_dims, table_positions, bias, value_norm, q_weight, k_weight, eps, (float*)q_out, (float*)k_cache,
                      (float*)v_cache, slot_mapping, heads, kv_heads, dim, vdim, page_size, total_pages, err);
 }

@@ -10,7 +10,13 @@
 //    starts at 0:  m_t = max(logf_t + m_(t-1), logi_t),  a_t = exp(logf_t + m_(t-1) - m_t),
 //    b_t = exp(logi_t - m_t);  o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + 1e-6).
 //
-// Kernels: short_conv_residual (+ tail update): out = x + causal convolution of x over time per
+//  * gated linear attention: a_t per head and channel from a low-rank map of the input,
+//    a_t = sigmoid(z_t)^(1 / tau) with z_t = W2 y_t + b (y_t the input's projection to a few
+//    numbers), taken as exp(logsigmoid(z_t) / tau); w_t = k_t, u_t = v_t; the read-out's gate is
+//    silu(.) instead of sigmoid(.).
+//
+// Kernels: lowrank_decay (a block takes eight tokens and 128 channels, so that a row of W2 is read
+// once per eight tokens); short_conv_residual (+ tail update): out = x + causal convolution of x over time per
 // channel, the last taps - 1 inputs kept per request; hgrn2_gates; mlstm_gates (a warp per request
 // and head walks the step's tokens in order); gated_recurrence (columns of S do not interact: a
 // block owns some columns of one head of one request, TPC lanes a column, tokens in order, eight at
@@ -143,6 +149,40 @@ mlstm_gates_kernel(const float* __restrict__ gi, const float* __restrict__ gf, i
         }
     }
     if (lane == 0) *m_ptr = m;
+}
+
+// grid: (blocks of LD_TOKENS tokens, blocks of 128 channels).  y: element (n, r) at [n * y_ld + r]; w2: [channels, rank];
+// decay: [N, channels] = exp(logsigmoid(w2 y + bias) * inv_tau).  A channel's sum runs over r in rising order.
+constexpr int LD_TOKENS = 8;
+__global__ void __launch_bounds__(128)
+lowrank_decay_kernel(const float* __restrict__ y, int y_ld, const float* __restrict__ w2,
+                     const float* __restrict__ bias, float inv_tau, float* __restrict__ decay, int num_tokens,
+                     int channels, int rank) {
+    extern __shared__ float ys[];  // [LD_TOKENS][rank]
+    ie_pdl_trigger();
+    ie_pdl_wait();
+    int n0 = blockIdx.x * LD_TOKENS;
+    int cnt = min(LD_TOKENS, num_tokens - n0);
+    for (int i = threadIdx.x; i < LD_TOKENS * rank; i += 128) {
+        int t = i / rank, r = i - t * rank;
+        ys[i] = t < cnt ? y[(size_t)(n0 + t) * y_ld + r] : 0.f;
+    }
+    __syncthreads();
+    int c = blockIdx.y * 128 + threadIdx.x;
+    if (c >= channels) return;
+    float acc[LD_TOKENS];
+#pragma unroll
+    for (int t = 0; t < LD_TOKENS; ++t) acc[t] = 0.f;
+    const float* wrow = w2 + (size_t)c * rank;
+    for (int r = 0; r < rank; ++r) {
+        float wv = wrow[r];
+#pragma unroll
+        for (int t = 0; t < LD_TOKENS; ++t) acc[t] = fmaf(wv, ys[t * rank + r], acc[t]);
+    }
+    float b = bias != nullptr ? bias[c] : 0.f;
+#pragma unroll
+    for (int t = 0; t < LD_TOKENS; ++t)
+        if (t < cnt) decay[(size_t)(n0 + t) * channels + c] = expf(logsigmoid_f(acc[t] + b) * inv_tau);
 }
 
 constexpr int GR_THREADS = 128;
@@ -298,13 +338,14 @@ gated_recurrence_kernel(const float* __restrict__ q, int q_ld, const float* __re
 
 // One warp per (token, head).  o: [rows, cols]; with `gates` the column `vdim` is n . q and the
 // row is first divided by max(|n . q|, exp(-m)) + 1e-6.  weight: [vdim] shared by the heads, or
-// [heads * vdim].  gate_pre (optional): element (n, head, d) at [n * gate_ld + head * vdim + d].
+// [heads * vdim].  gate_pre (optional): element (n, head, d) at [n * gate_ld + head * vdim + d]; the
+// row is multiplied by sigmoid(gate_pre), or by silu(gate_pre) with gate_silu.
 template <typename T>
 __global__ void __launch_bounds__(128)
 recurrence_readout_kernel(const float* __restrict__ o, int cols, const float* __restrict__ gates,
                           const float* __restrict__ weight, int weight_per_head, float eps,
-                          const float* __restrict__ gate_pre, int gate_ld, T* __restrict__ out, long long rows,
-                          int heads, int vdim) {
+                          const float* __restrict__ gate_pre, int gate_ld, int gate_silu, T* __restrict__ out,
+                          long long rows, int heads, int vdim) {
     ie_pdl_trigger();
     ie_pdl_wait();
     long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -325,7 +366,10 @@ recurrence_readout_kernel(const float* __restrict__ o, int cols, const float* __
     const float* wrow = weight + (weight_per_head ? (size_t)head * vdim : 0);
     for (int d = lane; d < vdim; d += 32) {
         float y = (src[d] / den) * inv * wrow[d];
-        if (gate_pre != nullptr) y *= sigmoid_f(gate_pre[n * gate_ld + (size_t)head * vdim + d]);
+        if (gate_pre != nullptr) {
+            float gp = gate_pre[n * gate_ld + (size_t)head * vdim + d];
+            y *= gate_silu ? silu_f(gp) : sigmoid_f(gp);
+        }
         ie_store(out + row * vdim + d, y);
     }
 }
@@ -380,6 +424,16 @@ IE_API int ie_short_conv_residual(const void* x, int dtype, const float* w, floa
                      state_stride, slots, cu_q, channels, taps, num_slots);
 }
 
+IE_API int ie_lowrank_decay(const float* y, int y_ld, const float* w2, const float* bias, float inv_tau,
+                            float* decay, int num_tokens, int channels, int rank, void* stream) {
+    if (num_tokens <= 0 || channels <= 0) return 0;
+    size_t smem = (size_t)LD_TOKENS * rank * sizeof(float);
+    if (rank < 1 || smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    dim3 grid((num_tokens + LD_TOKENS - 1) / LD_TOKENS, (channels + 127) / 128);
+    return ie_launch(lowrank_decay_kernel, grid, dim3(128), smem, (cudaStream_t)stream, y, y_ld, w2, bias, inv_tau,
+                     decay, num_tokens, channels, rank);
+}
+
 IE_API int ie_hgrn2_gates(float* proj, int ld, const float* bias, const float* lower, float* write,
                           int num_tokens, int size, void* stream) {
     size_t total = (size_t)num_tokens * size;
@@ -421,14 +475,14 @@ IE_API int ie_gated_recurrence(const float* q, int q_ld, const float* a, int a_l
 }
 
 IE_API int ie_recurrence_readout(const float* o, int cols, const float* gates, const float* weight,
-                                 int weight_per_head, float eps, const float* gate_pre, int gate_ld, void* out,
-                                 int out_dtype, long long rows, int heads, int vdim, void* stream) {
+                                 int weight_per_head, float eps, const float* gate_pre, int gate_ld, int gate_silu,
+                                 void* out, int out_dtype, long long rows, int heads, int vdim, void* stream) {
     if (rows <= 0) return 0;
     dim3 grid((unsigned)((rows + 3) / 4));
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == IE_BF16)
         return ie_launch(recurrence_readout_kernel<__nv_bfloat16>, grid, dim3(128), 0, s, o, cols, gates, weight,
-                         weight_per_head, eps, gate_pre, gate_ld, (__nv_bfloat16*)out, rows, heads, vdim);
+                         weight_per_head, eps, gate_pre, gate_ld, gate_silu, (__nv_bfloat16*)out, rows, heads, vdim);
     return ie_launch(recurrence_readout_kernel<float>, grid, dim3(128), 0, s, o, cols, gates, weight,
-                     weight_per_head, eps, gate_pre, gate_ld, (float*)out, rows, heads, vdim);
+                     weight_per_head, eps, gate_pre, gate_ld, gate_silu, (float*)out, rows, heads, vdim);
 }

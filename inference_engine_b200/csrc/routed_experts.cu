@@ -1,6 +1,7 @@
 // Kernels of the routed feed-forward (many small gated experts, a few per token).
 //
-//  * route_topk: per token the router's logits (32-bit), their softmax over all experts, the
+//  * route_topk: per token the router's logits (32-bit; plus a bias per expert if the router has
+//    one), their softmax over all experts, the
 //    groups' best scores, the kept groups, the `top` best allowed experts (ties: the lower index)
 //    and their scores divided by their sum (+ 1e-20).
 //  * routed_align: the step's (token, choice) pairs sorted by expert into tiles of TILE_M rows:
@@ -22,8 +23,8 @@ constexpr int ROUTE_THREADS = 256;
 
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_THREADS)
-route_topk_kernel(const T* __restrict__ x, const float* __restrict__ w, int width, int experts, int top,
-                  int groups, int keep, int* __restrict__ ids, float* __restrict__ weights) {
+route_topk_kernel(const T* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias, int width,
+                  int experts, int top, int groups, int keep, int* __restrict__ ids, float* __restrict__ weights) {
     extern __shared__ float sm[];  // x[width], score[experts], group_best[groups]
     float* xs = sm;
     float* score = xs + width;
@@ -48,7 +49,7 @@ route_topk_kernel(const T* __restrict__ x, const float* __restrict__ w, int widt
             for (int i = lane; i < width; i += 32) acc = fmaf(xs[i], we[i], acc);
         }
         acc = warp_sum(acc);
-        if (lane == 0) score[e] = acc;
+        if (lane == 0) score[e] = bias != nullptr ? acc + bias[e] : acc;
     }
     __syncthreads();
     if (warp != 0) return;
@@ -483,8 +484,8 @@ routed_bf16_kernel(const __nv_bfloat16* __restrict__ a_rows, const __nv_bfloat16
 }
 }  // namespace
 
-IE_API int ie_route_topk(const void* x, int dtype, const float* w, int num_tokens, int width, int experts, int top,
-                         int groups, int keep, int* ids, float* weights, void* stream) {
+IE_API int ie_route_topk(const void* x, int dtype, const float* w, const float* bias, int num_tokens, int width,
+                         int experts, int top, int groups, int keep, int* ids, float* weights, void* stream) {
     if (num_tokens <= 0) return 0;
     if (experts < 1 || groups < 1 || experts % groups || top < 1 || top > experts) return (int)cudaErrorInvalidValue;
     size_t smem = (size_t)(width + experts + groups) * sizeof(float);
@@ -492,9 +493,9 @@ IE_API int ie_route_topk(const void* x, int dtype, const float* w, int num_token
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == IE_BF16)
         return ie_launch(route_topk_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(ROUTE_THREADS), smem, s,
-                         (const __nv_bfloat16*)x, w, width, experts, top, groups, keep, ids, weights);
+                         (const __nv_bfloat16*)x, w, bias, width, experts, top, groups, keep, ids, weights);
     return ie_launch(route_topk_kernel<float>, dim3(num_tokens), dim3(ROUTE_THREADS), smem, s, (const float*)x, w,
-                     width, experts, top, groups, keep, ids, weights);
+                     bias, width, experts, top, groups, keep, ids, weights);
 }
 
 IE_API int ie_routed_tile_rows() { return TILE_M; }

@@ -10,6 +10,11 @@
 //    an order that depends on the row's width alone.
 //  * silu_mul_bias: out = silu(g + bg) * (u + bu) from rows that hold gates, then ups (32-bit, or the
 //    compute dtype); biases and activation in 32-bit.
+//  * gated_add_norm: h += sigmoid(gate_pre + gate_bias) * (sum of the parts of `delta`), element by
+//    element (a model whose sublayers enter the residual stream through a learned gate);
+//    out = rms(h) * w (if out).  One block per row, sums in an order that depends on the width alone.
+//  * polynorm: out = a N(z) + b N(z^2) + c N(z^3) + e per row, powers element by element,
+//    N(y) = y / sqrt(mean(y^2) + eps) over the row; sums and powers in 32-bit.
 //  * concat_cast: out[n] = [h[n]; x0[n]] in the compute dtype.
 //  * weighted_sum: out = sa * a + sb * b (32-bit).
 #include "common.cuh"
@@ -164,6 +169,83 @@ sandwich_norm_kernel(float* __restrict__ h, const float* __restrict__ delta, int
 #pragma unroll
         for (int v = 0; v < VEC; ++v) x.v[v] = w.v[v] * (x.v[v] * inv2);
         store_pack<VEC>(out + (size_t)r * hidden + i, x);
+    }
+}
+
+__device__ __forceinline__ float sigmoid_precise(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// gate_pre: [N, hidden] 32-bit (rows as in h); gate_bias: [hidden] or null.  `rows` selects rows and
+// leaves h as it is; out == null: only h is brought up to date.
+template <typename OutT, int VEC>
+__global__ void __launch_bounds__(SN_THREADS)
+gated_add_norm_kernel(float* __restrict__ h, const float* __restrict__ delta, int num_partials, size_t partial_stride,
+                      const float* __restrict__ gate_pre, const float* __restrict__ gate_bias,
+                      const float* __restrict__ weight, float eps, OutT* __restrict__ out,
+                      const int* __restrict__ rows, int hidden) {
+    extern __shared__ __align__(16) float row_buf[];  // [hidden]
+    __shared__ float red[SN_THREADS / 32];
+    ie_pdl_trigger();
+    ie_pdl_wait();
+    int r = blockIdx.x;
+    size_t src = (size_t)(rows ? rows[r] : r) * hidden;
+    float ss = 0.f;
+    for (int i = threadIdx.x * VEC; i < hidden; i += SN_THREADS * VEC) {
+        Pack<VEC> y = load_pack<VEC>(delta + src + i);
+        for (int p = 1; p < num_partials; ++p) {
+            Pack<VEC> d = load_pack<VEC>(delta + p * partial_stride + src + i);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) y.v[v] += d.v[v];
+        }
+        Pack<VEC> g = load_pack<VEC>(gate_pre + src + i), x = load_pack<VEC>(h + src + i);
+        if (gate_bias != nullptr) {
+            Pack<VEC> b = load_pack<VEC>(gate_bias + i);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) g.v[v] += b.v[v];
+        }
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+            x.v[v] = fmaf(sigmoid_precise(g.v[v]), y.v[v], x.v[v]);
+            ss = fmaf(x.v[v], x.v[v], ss);
+        }
+        store_pack<VEC>(row_buf + i, x);
+        if (rows == nullptr) store_pack<VEC>(h + src + i, x);
+    }
+    if (out == nullptr) return;
+    float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)hidden + eps);
+    for (int i = threadIdx.x * VEC; i < hidden; i += SN_THREADS * VEC) {
+        Pack<VEC> x = load_pack<VEC>(row_buf + i), w = load_pack<VEC>(weight + i);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) x.v[v] = w.v[v] * (x.v[v] * inv);
+        store_pack<VEC>(out + (size_t)r * hidden + i, x);
+    }
+}
+
+// One block per row of `z` ([N, width], 32-bit or the compute dtype); coeff: a, b, c, e.
+template <typename InT, typename OutT>
+__global__ void __launch_bounds__(SN_THREADS)
+polynorm_kernel(const InT* __restrict__ z, const float* __restrict__ coeff, float eps, OutT* __restrict__ out,
+                int width) {
+    extern __shared__ __align__(16) float row_buf[];  // [width]
+    __shared__ float red[SN_THREADS / 32];
+    ie_pdl_trigger();
+    ie_pdl_wait();
+    size_t at = (size_t)blockIdx.x * width;
+    float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+    for (int i = threadIdx.x; i < width; i += SN_THREADS) {
+        float x = ie_load(z + at + i), x2 = x * x, x3 = x2 * x;
+        row_buf[i] = x;
+        s2 += x2;
+        s4 = fmaf(x2, x2, s4);
+        s6 = fmaf(x3, x3, s6);
+    }
+    float n = (float)width;
+    float r1 = 1.0f / sqrtf(block_sum(s2, red) / n + eps);
+    float r2 = 1.0f / sqrtf(block_sum(s4, red) / n + eps);
+    float r3 = 1.0f / sqrtf(block_sum(s6, red) / n + eps);
+    float a = coeff[0] * r1, b = coeff[1] * r2, c = coeff[2] * r3, e = coeff[3];
+    for (int i = threadIdx.x; i < width; i += SN_THREADS) {
+        float x = row_buf[i];
+        ie_store(out + at + i, fmaf(x, fmaf(x, fmaf(x, c, b), a), e));
     }
 }
 
@@ -336,4 +418,64 @@ IE_API int ie_weighted_sum(const float* a, float sa, const float* b, float sb, f
     if (total <= 0) return 0;
     return ie_launch(weighted_sum_kernel, dim3(grid_for((size_t)total, 256)), dim3(256), 0, (cudaStream_t)stream, a,
                      sa, b, sb, out, (size_t)total);
+}
+
+// `delta` is the sum of `num_partials` arrays; `out` may be null (only h is brought up to date);
+// `rows` selects rows, and then h is not modified.
+IE_API int ie_gated_add_norm(float* h, const float* delta, int num_partials, long long partial_stride,
+                             const float* gate_pre, const float* gate_bias, const float* weight, float eps,
+                             void* out, int out_dtype, const int* rows, int num_rows, int hidden, void* stream) {
+    if (num_rows <= 0) return 0;
+    if (delta == nullptr || gate_pre == nullptr || num_partials < 1) return (int)cudaErrorInvalidValue;
+    if (out != nullptr && weight == nullptr) return (int)cudaErrorInvalidValue;
+    size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    cudaStream_t s = (cudaStream_t)stream;
+    bool vec = hidden % 4 == 0 && (size_t)partial_stride % 4 == 0 &&
+               ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(delta) |
+                 reinterpret_cast<uintptr_t>(gate_pre) | reinterpret_cast<uintptr_t>(gate_bias) |
+                 reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(out)) % 16 == 0);
+#define IE_GN_LAUNCH(T, V)                                                                                         \
+    do {                                                                                                           \
+        static IePerDevice allowed;                                                                                \
+        if (smem > 48 * 1024) {                                                                                    \
+            cudaError_t e = ie_allow_smem(allowed, gated_add_norm_kernel<T, V>, 200 * 1024);                       \
+            if (e != cudaSuccess) return (int)e;                                                                   \
+        }                                                                                                          \
+        return ie_launch(gated_add_norm_kernel<T, V>, dim3(num_rows), dim3(SN_THREADS), smem, s, h, delta,         \
+                         num_partials, (size_t)partial_stride, gate_pre, gate_bias, weight, eps, (T*)out, rows,    \
+                         hidden);                                                                                  \
+    } while (0)
+    if (out_dtype == IE_BF16) {
+        if (vec) IE_GN_LAUNCH(__nv_bfloat16, 4);
+        IE_GN_LAUNCH(__nv_bfloat16, 1);
+    }
+    if (vec) IE_GN_LAUNCH(float, 4);
+    IE_GN_LAUNCH(float, 1);
+#undef IE_GN_LAUNCH
+}
+
+// `z` is 32-bit or has the output's dtype.
+IE_API int ie_polynorm(const void* z, int in_dtype, const float* coeff, float eps, void* out, int out_dtype,
+                       int num_rows, int width, void* stream) {
+    if (num_rows <= 0 || width <= 0) return 0;
+    size_t smem = (size_t)width * sizeof(float);
+    if (smem > 200 * 1024 || (in_dtype != IE_F32 && in_dtype != out_dtype)) return (int)cudaErrorInvalidValue;
+    cudaStream_t s = (cudaStream_t)stream;
+#define IE_PN_LAUNCH(IN, OUT)                                                                                      \
+    do {                                                                                                           \
+        static IePerDevice allowed;                                                                                \
+        if (smem > 48 * 1024) {                                                                                    \
+            cudaError_t e = ie_allow_smem(allowed, polynorm_kernel<IN, OUT>, 200 * 1024);                          \
+            if (e != cudaSuccess) return (int)e;                                                                   \
+        }                                                                                                          \
+        return ie_launch(polynorm_kernel<IN, OUT>, dim3(num_rows), dim3(SN_THREADS), smem, s, (const IN*)z, coeff,  \
+                         eps, (OUT*)out, width);                                                                   \
+    } while (0)
+    if (out_dtype == IE_BF16) {
+        if (in_dtype == IE_BF16) IE_PN_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+        IE_PN_LAUNCH(float, __nv_bfloat16);
+    }
+    IE_PN_LAUNCH(float, float);
+#undef IE_PN_LAUNCH
 }

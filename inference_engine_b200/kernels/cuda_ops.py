@@ -199,7 +199,7 @@ class CudaOps:
     def _declare(self) -> None:
         P, I, F, L = c_void_p, c_int, c_float, ctypes.c_longlong
         sigs = {
-            "ie_embedding": [P, I, P, P, I, I, I, P, P],
+            "ie_embedding": [P, I, P, P, I, I, I, F, P, P],
             "ie_rmsnorm": [P, P, I, L, F, P, F, P, I, P, I, I, P],
             "ie_layernorm": [P, P, I, L, F, P, F, P, I, P, I, I, P],
             "ie_add_position_rows": [P, P, I, P, I, I, I, P, P],
@@ -213,13 +213,15 @@ class CudaOps:
             "ie_gemm_tma_bf16": [P, P, P, I, I, I, I, I, I, P, P],
             "ie_gemm_tc5_bf16": [P, P, P, I, I, I, I, I, I, P, P],
             "ie_gemm_tc5_ok": [I, I, I],
-            "ie_paged_attention_generic": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P, P],
+            "ie_paged_attention_generic": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P, P, I, P, P],
             "ie_sample": [P, I, I, P, P, P, P, P, P, I, P, P, P, P, P],
             "ie_bigram_embedding": [P, P, I, P, P, P, P, P, P, L, I, P, I, I, I, I, L, L, P, P],
             "ie_sandwich_norm": [P, P, I, L, P, P, F, P, F, P, I, P, I, I, P],
             "ie_silu_mul_bias": [P, I, P, P, I, I, I, P],
             "ie_concat_cast": [P, P, P, I, I, I, P],
             "ie_weighted_sum": [P, F, P, F, P, L, P],
+            "ie_gated_add_norm": [P, P, I, L, P, P, P, F, P, I, P, I, I, P],
+            "ie_polynorm": [P, I, P, F, P, I, I, I, P],
         }
         for name, args in sigs.items():
             fn = getattr(self.lib, name)
@@ -298,10 +300,11 @@ class CudaOps:
     # --- kernels ----------------------------------------------------------------------------
 
     @_kind("embedding")
-    def embedding(self, table, ids, out) -> None:
+    def embedding(self, table, ids, out, scale: float = 1.0) -> None:
+        """``out[n] = table[ids[n]] * scale`` as 32-bit rows."""
         self._check(self._embedding(table.data_ptr(), _dtype_code(table), ids.data_ptr(),
                                     out.data_ptr(), ids.shape[0], table.shape[1], table.shape[0],
-                                    self._err_ptr, self._stream()), "embedding")
+                                    float(scale), self._err_ptr, self._stream()), "embedding")
 
     @staticmethod
     def _partials(t) -> tuple[int, int]:
@@ -863,7 +866,7 @@ class CudaOps:
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q),
             block_tables.data_ptr(), block_tables.shape[1], ctx.seq_of_token.data_ptr(),
             ctx.positions.data_ptr(), out.data_ptr(), ctx.num_tokens, nh, nkv, hd, hd, hd, page_size,
-            k_cache.shape[0], scale, window, 0, None, self._err_ptr, self._stream()), "paged_attention")
+            k_cache.shape[0], scale, window, 0, None, None, None, 0, self._err_ptr, self._stream()), "paged_attention")
 
     @_kind("attention.latent")
     def latent_paged_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, value_dim,
@@ -898,7 +901,7 @@ class CudaOps:
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q),
             block_tables.data_ptr(), block_tables.shape[1], ctx.seq_of_token.data_ptr(),
             ctx.positions.data_ptr(), out.data_ptr(), ctx.num_tokens, nh, nkv, hd, value_dim,
-            v_cache.shape[-1], page_size, k_cache.shape[0], scale, window, 0, None, self._err_ptr,
+            v_cache.shape[-1], page_size, k_cache.shape[0], scale, window, 0, None, None, None, 0, self._err_ptr,
             self._stream()), "paged_attention_latent")
 
     # --- kernels of single mixers and feed-forwards (libraries built on first use) -------------
@@ -918,7 +921,7 @@ class CudaOps:
             "ie_gated_rms_heads": "P P F P P I L I P",
         },
         "routed": {
-            "ie_route_topk": "P I P I I I I I I P P P",
+            "ie_route_topk": "P I P P I I I I I I P P P",
             "ie_routed_max_tiles": "I I",
             "ie_routed_align": "P I I P P P I P",
             "ie_routed_gate_up": "P P P I P P P I I I I F I F F P",
@@ -929,10 +932,11 @@ class CudaOps:
             "ie_hgrn2_gates": "P I P P P I I P",
             "ie_mlstm_gates": "P P I P P F P L L P P P I I I P",
             "ie_gated_recurrence": "P I P I P I P P I P L P P P I I I I I F I P",
-            "ie_recurrence_readout": "P I P P I F P I P I L I I P",
+            "ie_recurrence_readout": "P I P P I F P I I P I L I I P",
+            "ie_lowrank_decay": "P I P P F P I I I P",
         },
         "gated_attn": {
-            "ie_qk_norm_rope_write": "P I P P I I P P F P P P I P I I I I I I I P P",
+            "ie_qk_norm_rope_write": "P I P P I I P I P P F P P P I P I I I I I I I P P",
         },
     }
 
@@ -1029,10 +1033,11 @@ class CudaOps:
             o.shape[0] * heads, vdim, self._stream()), "gated_rms_heads")
 
     @_kind("routed.route")
-    def route_topk(self, x, w_router, groups, keep, ids, weights) -> None:
-        """Softmax scores, group limit and the ``top`` experts per token with their normalised weights."""
+    def route_topk(self, x, w_router, groups, keep, ids, weights, bias=None) -> None:
+        """Softmax scores (of the router's logits plus ``bias``, if given), group limit and the ``top``
+        experts per token with their normalised weights."""
         self._check(self._part_lib("routed").ie_route_topk(
-            x.data_ptr(), _dtype_code(x), w_router.data_ptr(), x.shape[0], x.shape[1], w_router.shape[0],
+            x.data_ptr(), _dtype_code(x), w_router.data_ptr(), self._ptr(bias), x.shape[0], x.shape[1], w_router.shape[0],
             ids.shape[1], groups, keep, ids.data_ptr(), weights.data_ptr(), self._stream()), "route_topk")
 
     def routed_experts(self, x, ids, weights, w_gate_up, w_down, *, limit, alpha, up_offset, ws, tag="moe"):
@@ -1125,6 +1130,29 @@ class CudaOps:
         self._check(self._weighted_sum(a.data_ptr(), float(sa), b.data_ptr(), float(sb), out.data_ptr(), a.numel(),
                                        self._stream()), "weighted_sum")
 
+    @_kind("norm")
+    def gated_add_norm(self, h, delta, gate_pre, gate_bias, weight, eps, out, rows=None) -> None:
+        """``h += sigmoid(gate_pre + gate_bias) * delta`` element by element (not with ``rows``, which
+        selects rows and leaves ``h``); ``out = rms(h) * weight`` unless ``out`` is None.  ``delta`` may be
+        the parts of a split product (``[S, N, hidden]``); ``gate_pre``: 32-bit ``[N, hidden]``."""
+        if gate_pre.dtype != self.torch.float32 or gate_pre.shape != h.shape or not gate_pre.is_contiguous():
+            raise KernelError("gated_add_norm: the gate's pre-activation must be a 32-bit array like the stream")
+        n = h.shape[0] if rows is None else rows.shape[0]
+        parts, stride = self._partials(delta)
+        self._check(self._gated_add_norm(
+            h.data_ptr(), delta.data_ptr(), parts, stride, gate_pre.data_ptr(), self._ptr(gate_bias),
+            self._ptr(weight), eps, self._ptr(out), _dtype_code(out) if out is not None else 0, self._ptr(rows), n,
+            h.shape[1], self._stream()), "gated_add_norm")
+
+    @_kind("activation")
+    def polynorm(self, z, coeff, eps, out) -> None:
+        """``out = a N(z) + b N(z^2) + c N(z^3) + e`` per row with ``coeff = (a, b, c, e)`` and ``N`` the
+        division by the root mean square over the row; ``z`` is 32-bit or has ``out``'s dtype."""
+        if z.dtype not in (self.torch.float32, out.dtype) or z.shape != out.shape or not z.is_contiguous():
+            raise KernelError("polynorm reads contiguous rows, 32-bit or of the output's dtype")
+        self._check(self._polynorm(z.data_ptr(), _dtype_code(z), coeff.data_ptr(), eps, out.data_ptr(),
+                                   _dtype_code(out), z.shape[0], z.shape[1], self._stream()), "polynorm")
+
     # --- recurrent mixers with a decaying matrix state -------------------------------------------
 
     @_kind("recurrent.conv")
@@ -1176,30 +1204,51 @@ class CudaOps:
             state.shape[0], self._stream()), "gated_recurrence")
 
     @_kind("recurrent.out")
-    def recurrence_readout(self, o, gates, weight, eps, gate_pre, out, heads, vdim, cols) -> None:
+    def recurrence_readout(self, o, gates, weight, eps, gate_pre, out, heads, vdim, cols, gate_act="sigmoid") -> None:
         """Per (token, head): with ``gates`` divide by ``max(|o[vdim]|, exp(-m)) + 1e-6``; divide by the
         root mean square over ``vdim``; times ``weight`` (``[vdim]`` or ``[heads * vdim]``) and
-        ``sigmoid(gate_pre)`` (a view ``[N, heads * vdim]``) if given."""
+        ``sigmoid(gate_pre)`` (``gate_act="silu"``: ``silu(gate_pre)``; a view ``[N, heads * vdim]``) if given."""
+        if gate_act not in ("sigmoid", "silu"):
+            raise KernelError(f"recurrence_readout: no gate activation {gate_act!r}")
         per_head = 1 if weight.numel() == heads * vdim and heads > 1 else 0
         if weight.numel() not in (vdim, heads * vdim):
             raise KernelError("recurrence_readout: the weight fits neither a head nor all heads")
         self._check(self._part_lib("recurrent").ie_recurrence_readout(
             o.data_ptr(), cols, self._ptr(gates), weight.data_ptr(), per_head, eps, self._ptr(gate_pre),
-            0 if gate_pre is None else gate_pre.stride(0), out.data_ptr(), _dtype_code(out), o.shape[0] * heads,
-            heads, vdim, self._stream()), "recurrence_readout")
+            0 if gate_pre is None else gate_pre.stride(0), 1 if gate_act == "silu" else 0, out.data_ptr(),
+            _dtype_code(out), o.shape[0] * heads, heads, vdim, self._stream()), "recurrence_readout")
+
+    @_kind("recurrent.gates")
+    def lowrank_decay(self, y, w2, bias, tau: float, decay) -> None:
+        """``decay = sigmoid(y @ w2^T + bias) ** (1 / tau)`` as ``exp(logsigmoid(.) / tau)``, all 32-bit.
+        ``y``: a view ``[N, rank]`` of a projection; ``w2``: ``[channels, rank]``; ``decay``: ``[N, channels]``."""
+        if y.dtype != self.torch.float32 or w2.dtype != self.torch.float32 or y.stride(1) != 1:
+            raise KernelError("lowrank_decay reads a 32-bit projection and a 32-bit matrix")
+        self._check(self._part_lib("recurrent").ie_lowrank_decay(
+            y.data_ptr(), y.stride(0), w2.data_ptr(), self._ptr(bias), 1.0 / float(tau), decay.data_ptr(),
+            y.shape[0], w2.shape[0], w2.shape[1], self._stream()), "lowrank_decay")
 
     # --- attention with normalised queries and keys and sigmoid weights ---------------------------
 
     @_kind("rotary+cache")
     def qk_norm_rope_write(self, proj, positions, table, rot_dims, q_weight, k_weight, eps, q_out, k_cache,
-                           v_cache, slot_mapping, heads, kv_heads, dim, vdim, page_size) -> None:
+                           v_cache, slot_mapping, heads, kv_heads, dim, vdim, page_size, bias=None,
+                           value_norm: bool = False) -> None:
+        """The input stage of an attention with per-head norms (see ``csrc/gated_attention.cu``).
+        ``q_weight`` / ``k_weight`` None: queries and keys are not normalised; ``bias``: one row laid
+        out like the projection's first columns, added first; ``value_norm``: value heads are divided
+        by their root mean square.  ``proj`` may hold more columns behind the values."""
         if table is not None and table.shape[2] * 2 != rot_dims:
             raise KernelError("rotary table does not match the rotated dims")
-        if proj.dtype != self.torch.float32 or proj.shape[1] != (heads + kv_heads) * dim + kv_heads * vdim:
+        need = (heads + kv_heads) * dim + kv_heads * vdim
+        if proj.dtype != self.torch.float32 or proj.shape[1] < need or (q_weight is None) != (k_weight is None):
             raise KernelError("qk_norm_rope_write reads the fused 32-bit projection of queries, keys and values")
+        if bias is not None and (bias.dtype != self.torch.float32 or bias.numel() < need):
+            raise KernelError("qk_norm_rope_write: the bias must be a 32-bit row of the projection's width")
         self._check(self._part_lib("gated_attn").ie_qk_norm_rope_write(
             proj.data_ptr(), proj.stride(0), positions.data_ptr(), self._ptr(table), rot_dims,
-            0 if table is None else table.shape[0], self._ptr(q_weight), self._ptr(k_weight), eps, q_out.data_ptr(),
+            0 if table is None else table.shape[0], self._ptr(bias), 1 if value_norm else 0,
+            self._ptr(q_weight), self._ptr(k_weight), eps, q_out.data_ptr(),
             k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q_out), self._ptr(slot_mapping), proj.shape[0],
             heads, kv_heads, dim, vdim, page_size, k_cache.shape[0], self._err_ptr, self._stream()),
             "qk_norm_rope_write")
@@ -1243,8 +1292,24 @@ class CudaOps:
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q),
             block_tables.data_ptr(), block_tables.shape[1], ctx.seq_of_token.data_ptr(),
             ctx.positions.data_ptr(), out.data_ptr(), ctx.num_tokens, nh, nkv, hd, vdim, vdim, page_size,
-            k_cache.shape[0], scale, 0, int(chunk or 0), head_bias.data_ptr(), self._err_ptr, self._stream()),
-            "sigmoid_attention")
+            k_cache.shape[0], scale, 0, int(chunk or 0), head_bias.data_ptr(), None, None, 0, self._err_ptr,
+            self._stream()), "sigmoid_attention")
+
+    @_kind("attention.sink")
+    def sink_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, vdim, page_size, scale,
+                       window, sinks, gate, out) -> None:
+        """Softmax attention over the paged cache whose denominator also holds ``exp(sinks[head])`` (a
+        term without key or value; ``sinks`` None: a plain softmax), over the latest ``window``
+        positions (None or 0: all), with value rows of ``vdim`` entries; ``gate`` (a 32-bit view
+        ``[N, heads]``, or None): the head's result times ``sigmoid(gate)``."""
+        if gate is not None and (gate.dtype != self.torch.float32 or gate.stride(1) != 1):
+            raise KernelError("sink_attention: the output gate must be a 32-bit view with unit stride")
+        self._check(self._paged_attention_generic(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q),
+            block_tables.data_ptr(), block_tables.shape[1], ctx.seq_of_token.data_ptr(),
+            ctx.positions.data_ptr(), out.data_ptr(), ctx.num_tokens, nh, nkv, hd, vdim, vdim, page_size,
+            k_cache.shape[0], scale, int(window or 0), 0, None, self._ptr(sinks), self._ptr(gate),
+            0 if gate is None else gate.stride(0), self._err_ptr, self._stream()), "sink_attention")
 
     @_kind("activation")
     def silu_mul(self, gate_up, out, interleave: int = 0) -> None:

@@ -1,6 +1,6 @@
 from . import (  # noqa: F401 (register)
     attention, block, composite, delta_rule, embedding, feedforward, latent_attention, norm, position,
-    recurrent, routed, sigmoid_attention, stream,
+    recurrent, routed, sigmoid_attention, sink_attention, stream,
 )
 from .base import (
     Block,

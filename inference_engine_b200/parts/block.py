@@ -11,12 +11,18 @@ feed-forward's output as a pending ``delta`` for the next norm to add.
 next sublayer are one kernel: the block hands its last sublayer's raw output on as the pending delta
 together with what is to be done to it before the add (``output_post``: an output bias, if the
 sublayer has one, and the norm).
+
+``gated_prenorm_residual``: the pre-norm arrangement with a learned gate on each sublayer's way into
+the stream: ``x <- x + sigmoid(W1 h + b1) * mixer(h)`` with ``h = norm(x)``, then the same with
+``W2``, ``b2`` and the feed-forward.  The gate reads what the sublayer reads.  Its product runs in
+the compute dtype with 32-bit sums; sigmoid, multiplication and add are 32-bit and sit in the
+kernel of the next norm (the pending delta travels with its gate: ``output_post``).
 """
 
 from __future__ import annotations
 
-from .base import Block, BuildEnv, CacheBinding
-from .norm import PostNorm
+from .base import Block, BuildEnv, CacheBinding, WeightDecl
+from .norm import PostNorm, ResidualGate
 from .registry import build_part, register_part
 
 
@@ -86,4 +92,84 @@ class SandwichResidualBlock(Block):
             return mixed
         x = self.norms["pre_feed_forward"].add_norm(h, mixed, ctx, tag="norm.ffn",
                                                     delta_post=PostNorm(self.norms["post_mixer"]))
+        return self.feed_forward.forward(x, ctx)
+
+
+@register_part("block", "gated_prenorm_residual")
+class GatedPreNormResidualBlock(Block):
+    """Norms ``pre_mixer`` and, with a feed-forward, ``pre_feed_forward``.  Parameters: the tensor
+    names ``mixer_gate``, ``mixer_gate_bias``, ``feed_forward_gate``, ``feed_forward_gate_bias`` (a
+    bias name may be absent)."""
+
+    def __init__(self, mixer, feed_forward, pre_mixer, pre_feed_forward, names: dict, hidden_size: int, dtype) -> None:
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.pre_mixer, self.pre_feed_forward = pre_mixer, pre_feed_forward
+        self.names, self.hidden_size, self.dtype = dict(names), int(hidden_size), dtype
+        self.residual_mult = 1.0
+        self.w_gate: dict = {}
+        self.gate_bias: dict = {}
+        self._pending: ResidualGate | None = None
+
+    @classmethod
+    def from_spec(cls, params: dict, env: BuildEnv, *, layer, **_):
+        has_ff = layer.feed_forward is not None
+        names = {k: params[k] for k in ("mixer_gate", "mixer_gate_bias") if params.get(k)}
+        if has_ff:
+            names.update({k: params[k] for k in ("feed_forward_gate", "feed_forward_gate_bias") if params.get(k)})
+        for needed in ["mixer_gate"] + (["feed_forward_gate"] if has_ff else []):
+            if needed not in names:
+                raise ValueError(f"the gated block needs the tensor name {needed!r}")
+        return cls(
+            build_part("mixer", layer.mixer, env),
+            build_part("feed_forward", layer.feed_forward, env) if has_ff else None,
+            build_part("norm", layer.norms["pre_mixer"], env),
+            build_part("norm", layer.norms["pre_feed_forward"], env) if has_ff else None,
+            names, params.get("hidden_size", env.hidden_size), env.torch_dtype,
+        )
+
+    def parts(self):
+        both = [self.pre_mixer, self.mixer, self.pre_feed_forward, self.feed_forward]
+        return [p for p in both if p is not None]
+
+    def weights(self) -> dict[str, WeightDecl]:
+        h = self.hidden_size
+        out = {}
+        for which in ("mixer_gate", "feed_forward_gate"):
+            if which in self.names:
+                out[self.names[which]] = WeightDecl((h, h))
+            if which + "_bias" in self.names:
+                out[self.names[which + "_bias"]] = WeightDecl((h,), "vector")
+        return out
+
+    def bind(self, tensors, env: BuildEnv) -> None:
+        for which in ("mixer_gate", "feed_forward_gate"):
+            if which in self.names:
+                self.w_gate[which] = tensors[self.names[which]].to(self.dtype).contiguous()
+                bias = self.names.get(which + "_bias")
+                self.gate_bias[which] = tensors[bias].float().contiguous() if bias else None
+
+    def _gate(self, which: str, x, ctx) -> ResidualGate:
+        import torch
+
+        pre = ctx.ops.linear(x, self.w_gate[which], ws=ctx.ws, tag="resgate." + which, out_dtype=torch.float32)
+        return ResidualGate(pre, self.gate_bias[which])
+
+    @property
+    def output_post(self) -> ResidualGate:
+        """The gate of the delta this block's last forward left pending."""
+        return self._pending
+
+    def forward(self, h, delta, ctx, binding: CacheBinding | None, delta_scale: float = 1.0, delta_post=None):
+        if delta_post is None:
+            x = self.pre_mixer.add_norm(h, delta, ctx, tag="norm.mixer", delta_scale=delta_scale)
+        else:
+            x = self.pre_mixer.add_norm(h, delta, ctx, tag="norm.mixer", delta_scale=delta_scale,
+                                        delta_post=delta_post)
+        gate = self._gate("mixer_gate", x, ctx)
+        mixed = self.mixer.forward(x, ctx, binding)
+        if self.feed_forward is None:
+            self._pending = gate
+            return mixed
+        x = self.pre_feed_forward.add_norm(h, mixed, ctx, tag="norm.ffn", delta_post=gate)
+        self._pending = self._gate("feed_forward_gate", x, ctx)
         return self.feed_forward.forward(x, ctx)

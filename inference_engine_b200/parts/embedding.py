@@ -1,7 +1,7 @@
 """Token embedding and the output head.
 
-Embedding: ``x = table[token_ids]`` with no scaling (engine/model/llama.py:25,61); the rows
-are widened to the 32-bit residual stream.  Head: ``logits = x @ W^T`` in 32-bit out, no
+Embedding: ``x = table[token_ids]`` with no scaling (engine/model/llama.py:25,61), or times the
+constant ``scale`` of a model that has one; the rows are widened to the 32-bit residual stream.  Head: ``logits = x @ W^T`` in 32-bit out, no
 bias (engine/model/llama.py:36,68), times ``logit_scale`` where a model has one; with tied embeddings ``W`` is the embedding table
 itself (engine/model/loader.py:91-92), one buffer.
 """
@@ -16,13 +16,14 @@ from .registry import register_part
 class TokenEmbedding(Part):
     category = "embedding"
 
-    def __init__(self, weight: str, vocab_size: int, hidden_size: int, dtype) -> None:
+    def __init__(self, weight: str, vocab_size: int, hidden_size: int, dtype, scale: float = 1.0) -> None:
         self.weight_name, self.vocab_size, self.hidden_size = weight, vocab_size, hidden_size
-        self.dtype, self.table = dtype, None
+        self.dtype, self.table, self.scale = dtype, None, float(scale)
 
     @classmethod
     def from_spec(cls, params: dict, env: BuildEnv, **_):
-        return cls(params["weight"], params["vocab_size"], env.hidden_size, env.torch_dtype)
+        return cls(params["weight"], params["vocab_size"], env.hidden_size, env.torch_dtype,
+                   params.get("scale", 1.0))
 
     def weights(self) -> dict[str, WeightDecl]:
         return {self.weight_name: WeightDecl((self.vocab_size, self.hidden_size), "table")}
@@ -34,7 +35,10 @@ class TokenEmbedding(Part):
         import torch
 
         h = ctx.ws.buffer("residual", token_ids.shape[0], self.hidden_size, torch.float32)
-        ctx.ops.embedding(self.table, token_ids, h)
+        if self.scale == 1.0:
+            ctx.ops.embedding(self.table, token_ids, h)
+        else:
+            ctx.ops.embedding(self.table, token_ids, h, self.scale)
         return h
 
 

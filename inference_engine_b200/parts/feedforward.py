@@ -119,3 +119,42 @@ class SquaredReluFF(FeedForward):
         ctx.ops.relu_squared(up, act)
         return ctx.ops.linear(act, self.w_down, ws=ctx.ws, tag="ffn.delta", out_dtype=torch.float32,
                               allow_split=True)
+
+
+@register_part("feed_forward", "polynorm")
+class PolyNormFF(FeedForward):
+    """Dense feed-forward without a gate: ``down(act(up(x)))`` with ``act(z) = a N(z) + b N(z^2) +
+    c N(z^3) + e``: powers element by element, ``N`` divides a token's vector by its root mean square
+    (eps inside the root), and ``(a, b, c, e)`` is a tensor of four numbers.  The first product's
+    sums stay 32-bit for the activation, which rounds once to the compute dtype."""
+
+    def __init__(self, *, up_proj: str, down_proj: str, coeff: str, hidden_size: int, intermediate_size: int,
+                 eps: float, dtype) -> None:
+        self.names = {"up": up_proj, "down": down_proj, "coeff": coeff}
+        self.hidden_size, self.intermediate_size, self.eps, self.dtype = hidden_size, intermediate_size, float(eps), dtype
+        self.w_up = self.w_down = self.coeff = None
+
+    @classmethod
+    def from_spec(cls, params: dict, env: BuildEnv, **_):
+        return cls(up_proj=params["up_proj"], down_proj=params["down_proj"], coeff=params["coeff"],
+                   hidden_size=params.get("hidden_size", env.hidden_size),
+                   intermediate_size=params["intermediate_size"], eps=params["eps"], dtype=env.torch_dtype)
+
+    def weights(self) -> dict[str, WeightDecl]:
+        h, i = self.hidden_size, self.intermediate_size
+        return {self.names["up"]: WeightDecl((i, h)), self.names["down"]: WeightDecl((h, i)),
+                self.names["coeff"]: WeightDecl((4,), "vector", "ones_plus_normal")}
+
+    def bind(self, tensors, env: BuildEnv) -> None:
+        self.w_up = tensors[self.names["up"]].to(self.dtype).contiguous()
+        self.w_down = tensors[self.names["down"]].to(self.dtype).contiguous()
+        self.coeff = tensors[self.names["coeff"]].float().contiguous()
+
+    def forward(self, x, ctx):
+        import torch
+
+        up = ctx.ops.linear(x, self.w_up, ws=ctx.ws, tag="ffn.up32", out_dtype=torch.float32)
+        act = ctx.ws.buffer("ffn.act", x.shape[0], self.intermediate_size, self.dtype)
+        ctx.ops.polynorm(up, self.coeff, self.eps, act)
+        return ctx.ops.linear(act, self.w_down, ws=ctx.ws, tag="ffn.delta", out_dtype=torch.float32,
+                              allow_split=True)

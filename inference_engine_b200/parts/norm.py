@@ -38,12 +38,11 @@ class RMSNorm(Norm):
         n = h.shape[0] if rows is None else rows.shape[0]
         out = ctx.ws.buffer(tag, n, self.size, self.dtype)
         if delta_post is not None:
-            # the delta is normalised (and takes its bias) before it is added: one kernel for that,
-            # the add and this norm
+            # something is done to the delta before it is added (it is normalised and takes its bias,
+            # or passes a learned gate): one kernel for that, the add and this norm
             if delta_scale != 1.0:
-                raise ValueError("a delta that is normalised before the add has no residual multiplier")
-            ctx.ops.sandwich_norm(h, delta, delta_post.bias, delta_post.norm.weight, delta_post.norm.eps,
-                                  self.weight, self.eps, out, rows)
+                raise ValueError("a delta that is treated before the add has no residual multiplier")
+            delta_post.add_norm(h, delta, ctx, self.weight, self.eps, out, rows)
         elif delta_scale == 1.0:
             ctx.ops.rmsnorm(h, delta, self.weight, self.eps, out, rows)
         else:
@@ -58,9 +57,28 @@ class PostNorm:
     def __init__(self, norm: RMSNorm, bias=None) -> None:
         self.norm, self.bias = norm, bias
 
+    def add_norm(self, h, delta, ctx, weight, eps, out, rows) -> None:
+        """``h += norm(delta + bias)`` (not with ``rows``); ``out = rms(h) * weight``."""
+        ctx.ops.sandwich_norm(h, delta, self.bias, self.norm.weight, self.norm.eps, weight, eps, out, rows)
+
     def settle(self, h, delta, ctx) -> None:
         """``h += norm(delta + bias)`` with no normalised output."""
         ctx.ops.sandwich_norm(h, delta, self.bias, self.norm.weight, self.norm.eps, None, 0.0, None)
+
+
+class ResidualGate:
+    """A sublayer's output enters the residual stream through a gate: ``h += sigmoid(gate_pre + bias) *
+    delta`` element by element.  ``gate_pre`` is the 32-bit pre-activation ``[N, hidden]`` of this
+    step; carried beside the pending delta to whoever adds it, like :class:`PostNorm`."""
+
+    def __init__(self, gate_pre, bias=None) -> None:
+        self.gate_pre, self.bias = gate_pre, bias
+
+    def add_norm(self, h, delta, ctx, weight, eps, out, rows) -> None:
+        ctx.ops.gated_add_norm(h, delta, self.gate_pre, self.bias, weight, eps, out, rows)
+
+    def settle(self, h, delta, ctx) -> None:
+        ctx.ops.gated_add_norm(h, delta, self.gate_pre, self.bias, None, 0.0, None)
 
 
 @register_part("norm", "layer")

@@ -17,6 +17,12 @@ logi)``, ``S <- exp(logf + m - m') S + exp(logi - m') k v^T``, the normaliser ``
 ``k`` alone, ``o = S^T q / (max(|n . q|, exp(-m')) + 1e-6)``; each head's ``o`` is divided by its root
 mean square, the heads together are multiplied by a weight and by ``sigmoid(W_g h)``; ``W_o``.
 
+``gla``: gated linear attention with a decay per key channel.  ``q = W_q h * dim^-1/2``, ``k = W_k h``,
+``v = W_v h``; ``a = sigmoid(W_a2 (W_a1 h) + b)^(1 / tau)`` per head and channel, from a low-rank map of
+the input; ``S <- diag(a) S + k v^T``, ``o = S^T q``; each head's ``o`` is divided by its root mean
+square over ``vdim`` and multiplied by a weight of size ``vdim`` that the heads share; the heads
+together are multiplied by ``silu(W_g h)``; ``W_o``.
+
 Gates, decays, the state and the read-out are 32-bit in every precision; the projections run in
 the compute dtype with 32-bit sums.  The state lives in the request's state slot: ``S`` column by
 column (``[heads, columns, dim]``; the normaliser is one more column), then the maxima.
@@ -190,3 +196,67 @@ class MLSTM(Mixer):
         out = ws.buffer("mlstm.out", n, vs, self.dtype)
         ops.recurrence_readout(o, gates, self.out_norm, self.eps, proj[:, at_g: at_i], out, H, self.vdim, cols)
         return ops.linear(out, self.w_o, ws=ws, tag="mlstm.delta", out_dtype=f32, allow_split=self.allow_split)
+
+
+@register_part("mixer", "gla")
+class GatedLinearAttention(Mixer):
+    allow_split = True
+
+    def __init__(self, *, names: dict, hidden_size: int, heads: int, dim: int, vdim: int, rank: int, tau: float,
+                 eps: float, dtype) -> None:
+        if rank < 1 or not tau > 0:
+            raise ValueError("the decay's low-rank map needs a rank of at least 1 and a positive tau")
+        self.names, self.hidden_size = dict(names), hidden_size
+        self.heads, self.dim, self.vdim, self.rank = heads, dim, vdim, int(rank)
+        self.tau, self.eps, self.dtype = float(tau), float(eps), dtype
+        self.qk_size, self.v_size = heads * dim, heads * vdim
+        self.w_in = None
+
+    @classmethod
+    def from_spec(cls, params: dict, env: BuildEnv, **_):
+        return cls(names=params["names"], hidden_size=params.get("hidden_size", env.hidden_size),
+                   heads=params["heads"], dim=params["dim"], vdim=params["vdim"], rank=params["rank"],
+                   tau=params["tau"], eps=params["eps"], dtype=env.torch_dtype)
+
+    def weights(self) -> dict[str, WeightDecl]:
+        n, h = self.names, self.hidden_size
+        return {
+            n["q"]: WeightDecl((self.qk_size, h)), n["k"]: WeightDecl((self.qk_size, h)),
+            n["v"]: WeightDecl((self.v_size, h)), n["g"]: WeightDecl((self.v_size, h)),
+            n["a1"]: WeightDecl((self.rank, h)), n["a2"]: WeightDecl((self.qk_size, self.rank)),
+            n["a2_bias"]: WeightDecl((self.qk_size,), "vector"),
+            n["out_norm"]: WeightDecl((self.vdim,), "vector", "ones_plus_normal"),
+            n["o"]: WeightDecl((h, self.v_size)),
+        }
+
+    def bind(self, tensors, env: BuildEnv) -> None:
+        import torch
+
+        n = self.names
+        self.w_in = torch.cat([tensors[n[k]].to(self.dtype) for k in ("q", "k", "v", "g", "a1")]).contiguous()
+        self.w_o = tensors[n["o"]].to(self.dtype).contiguous()
+        self.w_a2 = tensors[n["a2"]].float().contiguous()  # the decay's second map stays 32-bit
+        self.a2_bias = tensors[n["a2_bias"]].float().contiguous()
+        self.out_norm = tensors[n["out_norm"]].float().contiguous()
+
+    def cache_request(self) -> StateRequest:
+        return StateRequest((self.heads * self.vdim * self.dim,))
+
+    def forward(self, x, ctx, binding):
+        import torch
+
+        f32, n, qk, vs = torch.float32, x.shape[0], self.qk_size, self.v_size
+        group = ctx.groups[binding.group]
+        ops, ws = ctx.ops, ctx.ws
+        proj = ops.linear(x, self.w_in, ws=ws, tag="gla.in", out_dtype=f32)
+        at_g, at_a = 2 * qk + vs, 2 * qk + 2 * vs
+        decay = ws.buffer("gla.decay", n, qk, f32)
+        ops.lowrank_decay(proj[:, at_a: at_a + self.rank], self.w_a2, self.a2_bias, self.tau, decay)
+        o = ws.buffer("gla.o", n, vs, f32)
+        ops.gated_recurrence(proj[:, :qk], decay, proj[:, qk: 2 * qk], None, proj[:, 2 * qk: at_g],
+                             group.state[binding.slot], group.slots, ctx, o, self.heads, self.dim, self.vdim,
+                             self.vdim, self.dim ** -0.5)
+        out = ws.buffer("gla.out", n, vs, self.dtype)
+        ops.recurrence_readout(o, None, self.out_norm, self.eps, proj[:, at_g: at_a], out, self.heads, self.vdim,
+                               self.vdim, gate_act="silu")
+        return ops.linear(out, self.w_o, ws=ws, tag="gla.delta", out_dtype=f32, allow_split=self.allow_split)

@@ -1,10 +1,11 @@
 """A feed-forward made of many small gated experts, of which every token uses a few.
 
-Routing: scores are the softmax over all experts of ``router(x)``, in 32-bit.  The experts form
+Routing: scores are the softmax over all experts of ``router(x)`` (plus a bias per expert, if the
+router has one: ``router_bias``), in 32-bit.  The experts form
 ``groups`` equal groups of neighbours; a group's score is its best expert's; only experts of the
 ``keep_groups`` best groups can be chosen (``groups = keep_groups = 1``: no such limit).  The
 ``top`` allowed experts with the largest scores are taken, and their scores, divided by their sum
-(+ 1e-20), weigh the experts' outputs.
+(+ 1e-20), weigh the experts' outputs (without groups this is the softmax over the chosen logits).
 
 An expert: ``g = min(gate(x), limit)``, ``u = clamp(up(x), -limit, limit)``,
 ``y = g * sigmoid(alpha * g) * (u + up_offset)``, output ``down(y)``; no biases.  ``limit``,
@@ -27,14 +28,15 @@ from .registry import register_part
 class RoutedExperts(FeedForward):
     def __init__(self, *, router: str, expert_prefix: str, experts: int, top: int, groups: int,
                  keep_groups: int, hidden_size: int, intermediate_size: int, limit: float | None,
-                 alpha: float, up_offset: float, dtype) -> None:
+                 alpha: float, up_offset: float, dtype, router_bias: str | None = None) -> None:
         if not 1 <= top <= experts:
             raise ValueError(f"top ({top}) must be between 1 and the number of experts ({experts})")
         if groups < 1 or experts % groups or not 1 <= keep_groups <= groups:
             raise ValueError(f"{experts} experts cannot form {groups} equal groups of which {keep_groups} are kept")
         if top > keep_groups * (experts // groups):
             raise ValueError(f"top ({top}) exceeds the experts of the {keep_groups} kept groups")
-        self.router_name, self.expert_prefix = router, expert_prefix
+        self.router_name, self.expert_prefix, self.router_bias_name = router, expert_prefix, router_bias
+        self.router_bias = None
         self.experts, self.top, self.groups, self.keep_groups = experts, top, groups, keep_groups
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.limit = None if limit is None else float(limit)
@@ -49,7 +51,7 @@ class RoutedExperts(FeedForward):
                    hidden_size=params.get("hidden_size", env.hidden_size),
                    intermediate_size=params["intermediate_size"], limit=params.get("limit"),
                    alpha=params.get("alpha", 1.702), up_offset=params.get("up_offset", 1.0),
-                   dtype=env.torch_dtype)
+                   dtype=env.torch_dtype, router_bias=params.get("router_bias"))
 
     def _name(self, e: int, which: str) -> str:
         return f"{self.expert_prefix}{e}.{which}"
@@ -57,6 +59,8 @@ class RoutedExperts(FeedForward):
     def weights(self) -> dict[str, WeightDecl]:
         h, i = self.hidden_size, self.intermediate_size
         out = {self.router_name: WeightDecl((self.experts, h), "vector")}
+        if self.router_bias_name is not None:
+            out[self.router_bias_name] = WeightDecl((self.experts,), "vector")
         for e in range(self.experts):
             out[self._name(e, "gate")] = WeightDecl((i, h))
             out[self._name(e, "up")] = WeightDecl((i, h))
@@ -67,6 +71,8 @@ class RoutedExperts(FeedForward):
         import torch
 
         self.w_router = tensors[self.router_name].float().contiguous()  # routing is 32-bit
+        if self.router_bias_name is not None:
+            self.router_bias = tensors[self.router_bias_name].float().contiguous()
         self.w_gate_up = torch.stack([
             torch.stack([tensors[self._name(e, "gate")].to(self.dtype), tensors[self._name(e, "up")].to(self.dtype)])
             for e in range(self.experts)]).contiguous()
@@ -79,7 +85,10 @@ class RoutedExperts(FeedForward):
         n = x.shape[0]
         ids = ctx.ws.buffer("moe.ids", n, self.top, torch.int32)
         weights = ctx.ws.buffer("moe.weights", n, self.top, torch.float32)
-        ctx.ops.route_topk(x, self.w_router, self.groups, self.keep_groups, ids, weights)
+        if self.router_bias is None:
+            ctx.ops.route_topk(x, self.w_router, self.groups, self.keep_groups, ids, weights)
+        else:
+            ctx.ops.route_topk(x, self.w_router, self.groups, self.keep_groups, ids, weights, bias=self.router_bias)
         return ctx.ops.routed_experts(x, ids, weights, self.w_gate_up, self.w_down,
                                       limit=self.limit, alpha=self.alpha, up_offset=self.up_offset,
                                       ws=ctx.ws, tag="moe")

@@ -14,8 +14,8 @@ import torch
 class RefOps:
     name = "torch-reference"
 
-    def embedding(self, table, ids, out):
-        out.copy_(table[ids.long()].float())
+    def embedding(self, table, ids, out, scale=1.0):
+        out.copy_(table[ids.long()].float() * scale)
 
     @staticmethod
     def _added(h, delta, rows, delta_scale):
@@ -141,9 +141,10 @@ class RefOps:
 
     # --- routed experts -----------------------------------------------------------------------
 
-    def route_topk(self, x, w_router, groups, keep, ids, weights):
+    def route_topk(self, x, w_router, groups, keep, ids, weights, bias=None):
         n, experts, top = x.shape[0], w_router.shape[0], ids.shape[1]
-        s = (x.float() @ w_router.t()).softmax(-1)
+        logits = x.float() @ w_router.t()
+        s = (logits if bias is None else logits + bias).softmax(-1)
         per = experts // groups
         best = s.view(n, groups, per).max(-1).values
         allowed = torch.zeros(n, groups, dtype=torch.bool)
@@ -277,7 +278,13 @@ class RefOps:
                 o[t] = torch.einsum("hdc,hd->hc", S, qt) * q_scale
             state[slot, :matrix] = S.transpose(1, 2).reshape(-1)
 
-    def recurrence_readout(self, o, gates, weight, eps, gate_pre, out, heads, vdim, cols):
+    def lowrank_decay(self, y, w2, bias, tau, decay):
+        z = y.float() @ w2.t()
+        if bias is not None:
+            z = z + bias
+        decay.copy_(torch.exp(torch.nn.functional.logsigmoid(z) / tau))
+
+    def recurrence_readout(self, o, gates, weight, eps, gate_pre, out, heads, vdim, cols, gate_act="sigmoid"):
         x = o.view(-1, heads, cols)
         y = x[..., :vdim]
         if gates is not None:
@@ -286,19 +293,28 @@ class RefOps:
         y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps)
         y = y * (weight.view(heads, vdim) if weight.numel() == heads * vdim else weight)
         if gate_pre is not None:
-            y = y * torch.sigmoid(gate_pre.float().reshape(-1, heads, vdim))
+            g = gate_pre.float().reshape(-1, heads, vdim)
+            y = y * (torch.sigmoid(g) if gate_act == "sigmoid" else g * torch.sigmoid(g))
         out.copy_(y.reshape(out.shape).to(out.dtype))
 
     # --- attention with normalised queries and keys and sigmoid weights ---------------------------
 
     def qk_norm_rope_write(self, proj, positions, table, rot_dims, q_weight, k_weight, eps, q_out, k_cache,
-                           v_cache, slot_mapping, heads, kv_heads, dim, vdim, page_size):
+                           v_cache, slot_mapping, heads, kv_heads, dim, vdim, page_size, bias=None,
+                           value_norm=False):
         n = proj.shape[0]
-        q = proj[:, : heads * dim].reshape(n, heads, dim).float()
-        k = proj[:, heads * dim: (heads + kv_heads) * dim].reshape(n, kv_heads, dim).float()
-        v = proj[:, (heads + kv_heads) * dim:].reshape(n, kv_heads, vdim).float()
-        q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight
-        k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_weight
+        end = (heads + kv_heads) * dim + kv_heads * vdim
+        proj = proj[:, :end].float()
+        if bias is not None:
+            proj = proj + bias[:end]
+        q = proj[:, : heads * dim].reshape(n, heads, dim)
+        k = proj[:, heads * dim: (heads + kv_heads) * dim].reshape(n, kv_heads, dim)
+        v = proj[:, (heads + kv_heads) * dim:].reshape(n, kv_heads, vdim)
+        if q_weight is not None:
+            q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight
+            k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_weight
+        if value_norm:
+            v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)
         if table is not None and rot_dims > 0:
             half = rot_dims // 2
             cos, sin = table[positions.long(), 0][:, None, :], table[positions.long(), 1][:, None, :]
@@ -331,6 +347,50 @@ class RefOps:
             scores = torch.einsum("hd,khd->hk", q[t].reshape(nh, hd).float(), k) * scale
             weights = torch.sigmoid(scores + head_bias[:, None])
             out[t] = torch.einsum("hk,khd->hd", weights, v).reshape(nh * vdim).to(out.dtype)
+
+    def sink_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, vdim, page_size, scale,
+                       window, sinks, gate, out):
+        groups = nh // nkv
+        tables = block_tables.long().cpu()
+        positions = ctx.positions.cpu().tolist()
+        seqs = ctx.seq_of_token.cpu().tolist()
+        for t in range(ctx.num_tokens):
+            p, s = positions[t], seqs[t]
+            lo = max(0, p - window + 1) if window else 0
+            keys = torch.arange(lo, p + 1)
+            pages, offs = tables[s][keys // page_size], keys % page_size
+            k = k_cache[pages, :, offs].float().repeat_interleave(groups, dim=1)  # [keys, nh, hd]
+            v = v_cache[pages, :, offs].float().repeat_interleave(groups, dim=1)
+            scores = torch.einsum("hd,khd->hk", q[t].reshape(nh, hd).float(), k) * scale
+            if sinks is not None:
+                scores = torch.cat([scores, sinks[:, None]], dim=1)
+            weights = scores.softmax(-1)[:, : keys.numel()]
+            o = torch.einsum("hk,khd->hd", weights, v)
+            if gate is not None:
+                o = o * torch.sigmoid(gate[t].float())[:, None]
+            out[t] = o.reshape(nh * vdim).to(out.dtype)
+
+    def gated_add_norm(self, h, delta, gate_pre, gate_bias, weight, eps, out, rows=None):
+        if delta.dim() == 3:
+            delta = delta.sum(0)
+        g = gate_pre if gate_bias is None else gate_pre + gate_bias
+        if rows is None:
+            h.add_(torch.sigmoid(g) * delta)
+            x = h
+        else:
+            r = rows.long()
+            x = h[r] + torch.sigmoid(g[r]) * delta[r]
+        if out is not None:
+            out.copy_((weight * (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps))).to(out.dtype))
+
+    def polynorm(self, z, coeff, eps, out):
+        x = z.float()
+        a, b, c, e = coeff.tolist()
+
+        def unit(y):
+            return y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps)
+
+        out.copy_((a * unit(x) + b * unit(x * x) + c * unit(x * x * x) + e).to(out.dtype))
 
     def linear(self, x, w, out=None, *, ws=None, tag="linear", out_dtype=None, allow_split=False):
         if out is None:
