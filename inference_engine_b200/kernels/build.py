@@ -161,6 +161,16 @@ def build_sigmoid_attention(dim: int, vdim: int) -> Path:
                          [f"-DSA_D={dim}", f"-DSA_DV={vdim}"])
 
 
+def build_sink_attention(dim: int, vdim: int) -> Path:
+    """The tensor-core softmax attention with a sink, a window and head gates for one pair of key and
+    value sizes (compiled on first use for the sizes the loaded model has)."""
+    if dim % 16 or vdim % 16 or not 16 <= dim <= 256 or not 16 <= vdim <= 256:
+        raise BuildError(f"the tensor-core sink attention takes sizes that are multiples of 16 up to 256, "
+                         f"not {dim} and {vdim}")
+    return build_library(f"ie_b200_sinkattn_d{dim}_v{vdim}", ["sink_attention_mma.cu"],
+                         [f"-DSK_D={dim}", f"-DSK_DV={vdim}"])
+
+
 # Kernels only some mixers and feed-forwards need, each a library of its own that is built the
 # first time a model with such a part runs: name -> sources.
 PART_LIBRARIES = {
@@ -189,7 +199,7 @@ def build_all(prune: bool = True) -> list[Path]:
     with ThreadPoolExecutor(max_workers=os.cpu_count() or 2) as pool:
         libs += list(pool.map(build_attention, ATTENTION_HEAD_DIMS))
         libs += list(pool.map(build_part_library, PART_LIBRARIES))
-        libs += [build_sigmoid_attention(64, 64)]
+        libs += [build_sigmoid_attention(64, 64), build_sink_attention(64, 64)]
     if prune:
         keep = {lib.name for lib in libs}
         for old in build_dir().glob("libie_b200_*.so"):

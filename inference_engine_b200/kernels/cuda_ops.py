@@ -18,7 +18,7 @@ import os
 from ctypes import c_float, c_int, c_void_p
 
 from .build import (ATTENTION_HEAD_DIMS, build_attention, build_core, build_part_library,
-                    build_sigmoid_attention)
+                    build_sigmoid_attention, build_sink_attention)
 
 _ERRORS = {
     1: "a token id outside the vocabulary",
@@ -125,6 +125,8 @@ class CudaOps:
         self._attn_libs: dict[int, object] = {}
         self._part_libs: dict[str, object] = {}
         self._sigattn_libs: dict[tuple[int, int], object] = {}
+        self._sinkattn_libs: dict[tuple[int, int], object] = {}
+        self.sink_mma = os.environ.get("IE_B200_SINK_MMA", "1") != "0"  # tensor-core sink attention
         self.sigmoid_mma = os.environ.get("IE_B200_SIGMOID_MMA", "1") != "0"  # tensor-core sigmoid attention
         self._argmax_scratch = None
         self._tickets = None
@@ -1295,15 +1297,46 @@ class CudaOps:
             k_cache.shape[0], scale, 0, int(chunk or 0), head_bias.data_ptr(), None, None, 0, self._err_ptr,
             self._stream()), "sigmoid_attention")
 
+    def _sink_attention_lib(self, hd: int, vdim: int):
+        lib = self._sinkattn_libs.get((hd, vdim))
+        if lib is None:
+            path = build_sink_attention(hd, vdim)
+            try:
+                lib = ctypes.CDLL(str(path))
+            except OSError as exc:
+                raise KernelError(f"the kernel library {path} could not be loaded: {exc}") from exc
+            P, I, F = c_void_p, c_int, c_float
+            lib.ie_sink_attention_mma.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P, I, P, P]
+            lib.ie_sink_attention_mma.restype = c_int
+            self._sinkattn_libs[(hd, vdim)] = lib
+        return lib
+
     @_kind("attention.sink")
     def sink_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, vdim, page_size, scale,
                        window, sinks, gate, out) -> None:
         """Softmax attention over the paged cache whose denominator also holds ``exp(sinks[head])`` (a
         term without key or value; ``sinks`` None: a plain softmax), over the latest ``window``
         positions (None or 0: all), with value rows of ``vdim`` entries; ``gate`` (a 32-bit view
-        ``[N, heads]``, or None): the head's result times ``sigmoid(gate)``."""
+        ``[N, heads]``, or None): the head's result times ``sigmoid(gate)``.  bfloat16 with key and
+        value sizes that are multiples of 16 up to 256 runs the tensor-core kernel (a block per 64
+        positions of a request and head, for prompt portions and single tokens; lengths and tables
+        are read on the device, and a captured step is launched for the most tokens a request can
+        bring within its bounds); 32-bit and other sizes the general kernel.  Neither kernel's
+        order of operations depends on the batch."""
         if gate is not None and (gate.dtype != self.torch.float32 or gate.stride(1) != 1):
             raise KernelError("sink_attention: the output gate must be a 32-bit view with unit stride")
+        if (self.sink_mma and q.dtype == self.torch.bfloat16 and hd % 16 == 0 and vdim % 16 == 0
+                and 16 <= hd <= 256 and 16 <= vdim <= 256 and page_size & (page_size - 1) == 0):
+            lib = self._sink_attention_lib(hd, vdim)
+            bounds = getattr(ctx, "bounds", None)
+            longest = bounds[0] if bounds is not None else ctx.max_q_len  # (a captured step: its token bound)
+            self._check(lib.ie_sink_attention_mma(
+                q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
+                block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(), ctx.num_seqs,
+                longest, nh, nkv, page_size, k_cache.shape[0], scale, int(window or 0), self._ptr(sinks),
+                self._ptr(gate), 0 if gate is None else gate.stride(0), self._err_ptr, self._stream()),
+                "sink_attention_mma")
+            return
         self._check(self._paged_attention_generic(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q),
             block_tables.data_ptr(), block_tables.shape[1], ctx.seq_of_token.data_ptr(),

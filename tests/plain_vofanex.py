@@ -41,7 +41,8 @@ def attention(h, W, p, m, eps):
     v = rms((h @ W[p + ".v"].T + W[p + ".v.b"]).view(T, G, dv), eps)
     group = torch.arange(H) // (H // G)
     scores = torch.einsum("thd,shd->hts", q, k[:, group]) * m["scale"]
-    weights = sink_window_softmax(scores, W[p + ".sink"], m["mask"]["size"])
+    window = (m.get("mask") or {}).get("size") or T  # (no mask: every earlier position is seen)
+    weights = sink_window_softmax(scores, W[p + ".sink"], window)
     o = torch.einsum("hts,shv->thv", weights, v[:, group])
     gate = torch.sigmoid(h @ W[p + ".g"].T)  # [T, H]
     return (o * gate[..., None]).reshape(T, H * dv) @ W[p + ".o"].T
@@ -92,7 +93,19 @@ def expert(h, W, p):
     return ((g * torch.sigmoid(g)) * (h @ W[p + ".up"].T)) @ W[p + ".down"].T
 
 
-def moe_ff(h, W, p, mlp):
+def router_margin(h, W, p, top):
+    """The smallest gap, over the tokens, between the last chosen logit and the best one not chosen
+    (infinite when every expert is chosen): how far the choice is from a close call."""
+    z = h @ W[p + ".router"].T + W[p + ".router.b"]
+    if top >= z.shape[-1]:
+        return float("inf")
+    best = torch.topk(z, top + 1, dim=-1).values
+    return float((best[:, top - 1] - best[:, top]).min())
+
+
+def moe_ff(h, W, p, mlp, margins=None):
+    if margins is not None:
+        margins.append(router_margin(h, W, p, mlp["router"]["top"]))
     ids, weights = route(h, W, p, mlp["router"]["top"])
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
@@ -105,7 +118,7 @@ def residual_gate(h, W, name):
     return torch.sigmoid(h @ W[name].T + W[name + ".b"])
 
 
-def layer(x, W, i, entry, eps):
+def layer(x, W, i, entry, eps, margins=None):
     p = f"l{i}"
     h = rms(x, eps) * W[p + ".norm1"]
     mix = attention if entry["type"] == "attention" else gla
@@ -114,16 +127,16 @@ def layer(x, W, i, entry, eps):
     if mlp is None:
         return x
     h = rms(x, eps) * W[p + ".norm2"]
-    y = dense_ff(h, W, p + ".mlp", eps) if mlp["kind"] == "dense" else moe_ff(h, W, p + ".mlp", mlp)
+    y = dense_ff(h, W, p + ".mlp", eps) if mlp["kind"] == "dense" else moe_ff(h, W, p + ".mlp", mlp, margins)
     return x + residual_gate(h, W, p + ".rg2") * y
 
 
-def forward(cfg, weights, tokens, dtype=torch.float64, layers_out=None):
+def forward(cfg, weights, tokens, dtype=torch.float64, layers_out=None, margins=None):
     W = {n: (t.to(dtype) if t.is_floating_point() else t) for n, t in weights.items()}
     eps = cfg["norm"]["eps"]
     x = embed(tokens, W, cfg)
     for i, entry in enumerate(cfg["layers"]):
-        x = layer(x, W, i, entry, eps)
+        x = layer(x, W, i, entry, eps, margins)
         if layers_out is not None:
             layers_out.append(x.clone())
     return (rms(x, eps) * W["final.norm"]) @ W["head"].T
