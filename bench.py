@@ -565,6 +565,73 @@ def ravapel_rows(size: str, kinds: dict, peaks: dict, tokens: int, batch: int, c
         rows[kind] = out
     return rows
 
+# --- the Vofanex design beside the closest models ------------------------------------------------
+
+VOFANEX_SIZES = {
+    # width, (gla: heads, dim, vdim, rank, tau), (attention: heads, kv_heads, dim, vdim, window),
+    # dense ff, (experts: ff, count, top)
+    "w1024": (1024, (8, 128, 128, 16, 16.0), (16, 4, 64, 64, 512), 4096, (512, 16, 4)),
+    "w2048": (2048, (16, 128, 128, 32, 16.0), (16, 4, 128, 128, 1024), 8192, (1024, 32, 4)),
+}
+
+
+def vofanex_config(size: str) -> dict:
+    width, gl, at, ff, ex = VOFANEX_SIZES[size]
+    gla = {"heads": gl[0], "dim": gl[1], "vdim": gl[2], "decay_rank": gl[3], "tau": gl[4]}
+    attention = {"heads": at[0], "kv_heads": at[1], "dim": at[2], "vdim": at[3], "scale": at[2] ** -0.5,
+                 "mask": {"size": at[4]}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": ex[0]}, "router": {"experts": ex[1], "top": ex[2]}}
+    layers = [("gla", gla, dense), ("attention", attention, moe), ("attention", attention, dense), ("gla", gla, moe)]
+    return {"architecture": "Vofanex", "vocab": DESIGN_VOCAB, "width": width, "max_positions": MAX_CONTEXT,
+            "norm": {"eps": 1e-6}, "embedding": {"scale": 2.0},
+            "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in layers]}
+
+
+def vofanex_rows(size: str, kinds: dict, peaks: dict, tokens: int, batch: int, ctx: float, decode: bool) -> dict:
+    """Per kind of kernel of the Vofanex model: microseconds per launch and, where the kind has such a
+    figure, what it is of the measured peak: decode launches against the copy rate for the bytes they
+    must read (weights, the window's cached rows, state read and written), prompt launches against
+    the burst bf16 rate for their flops (the recurrence and 32-bit stages: the time only)."""
+    width, gl, at, ff, ex = VOFANEX_SIZES[size]
+    H, G, d, dv, window = at
+    eff, experts, top = ex
+    used = min(experts, batch * top if decode else experts)
+    weights = {  # elements of the matrix a launch reads
+        "linear:gla.in": width * (gl[0] * (2 * gl[1] + 2 * gl[2]) + gl[3]), "linear:gla.delta": width * gl[0] * gl[2],
+        "linear:sinkattn.in": width * ((H + G) * d + G * dv + H), "linear:sinkattn.delta": width * H * dv,
+        "linear:resgate.mixer_gate": width * width, "linear:resgate.feed_forward_gate": width * width,
+        "linear:ffn.up32": width * ff, "linear:ffn.delta": width * ff, "linear:head": width * DESIGN_VOCAB,
+        "routed.gate_up": 2 * eff * width * used, "routed.down": eff * width * used,
+    }
+    flops = {  # per prompt launch
+        "attention.sink": 2.0 * tokens * (min(window, tokens) - min(window, tokens) ** 2 / (2.0 * tokens)) * H * (d + dv),
+        "routed.gate_up": 2.0 * tokens * top * 2 * eff * width, "routed.down": 2.0 * tokens * top * eff * width,
+    }
+    state = gl[0] * gl[1] * gl[2]  # floats of a layer's state per request, read and written
+    rows = {}
+    for kind, r in kinds.items():
+        us = r["ms"] / r["launches"] * 1e3
+        out = {"us": round(us, 2), "launches": r["launches"]}
+        if decode:
+            nbytes = None
+            if weights.get(kind):
+                nbytes = 2 * weights[kind]
+            elif kind == "attention.sink":
+                nbytes = batch * min(ctx, window) * G * (d + dv) * 2
+            elif kind == "recurrent.rule":
+                nbytes = batch * state * 4 * 2
+            if nbytes:
+                out.update(gbs=round(nbytes / (us * 1e-6) / 1e9, 1),
+                           frac=round(nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 4))
+        else:
+            f = flops.get(kind) or (2.0 * tokens * weights[kind] if weights.get(kind) and kind != "linear:head" else None)
+            if f:
+                out.update(tflops=round(f / (us * 1e-6) / 1e12, 1),
+                           frac=round(f / (us * 1e-6) / 1e12 / peaks["bf16_tflops"], 4))
+        rows[kind] = out
+    return rows
+
 
 def run_design(args) -> dict:
     """`--design rugedra`: prompt and decode throughput of the Rugedra design at layer sizes of a real
@@ -572,7 +639,10 @@ def run_design(args) -> dict:
     delta rule + dense; random weights), beside a Llama model of the same width, depth, feed-forward
     size and vocabulary, and every kind of kernel of both by itself.  `--design ravapel`: the Ravapel
     design (four layers: HGRN2, two of attention beside a matrix memory, HGRN2, all with a dense
-    feed-forward; the middle two as a loop of one pass) beside the Rugedra and the Llama model."""
+    feed-forward; the middle two as a loop of one pass) beside the Rugedra and the Llama model.
+    `--design vofanex`: the Vofanex design (four layers: gated linear attention + dense, windowed sink
+    attention + experts, windowed sink attention + dense, gated linear attention + experts) beside
+    the Ravapel and the Llama model."""
     import torch
 
     from inference_engine_b200.engine.llm_engine import LLMEngine
@@ -590,6 +660,9 @@ def run_design(args) -> dict:
         models = [("rugedra", rugedra_config(size)), ("llama", llama_config_like(size))]
         if args.design == "ravapel":
             models.insert(0, ("ravapel", ravapel_config(size)))
+        elif args.design == "vofanex":
+            models = [("vofanex", vofanex_config(size)), ("ravapel", ravapel_config(size)),
+                      ("llama", llama_config_like(size))]
         for name, cfg in models:
             engine = LLMEngine.from_random(
                 cfg, seed=0, dtype="bfloat16", device="cuda", max_model_len=MAX_CONTEXT,
@@ -602,7 +675,10 @@ def run_design(args) -> dict:
                    "prefill_tokens_per_s": round(PREFILL_LEN / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
                    # (the prompt step is launched eagerly: what its kernels take by themselves, without the host)
                    "prefill_kernels_ms": round(sum(r["ms"] for r in kinds_prefill.values()), 3)}
-            if name == "ravapel":
+            if name == "vofanex":
+                row["kernels"] = {f"decode_b{batch}": vofanex_rows(size, kinds, peaks, batch, batch, ctx, True),
+                                  f"prefill_{PREFILL_LEN}": vofanex_rows(size, kinds_prefill, peaks, PREFILL_LEN, 1, PREFILL_LEN, False)}
+            elif name == "ravapel":
                 row["kernels"] = {f"decode_b{batch}": ravapel_rows(size, kinds, peaks, batch, batch, ctx, True),
                                   f"prefill_{PREFILL_LEN}": ravapel_rows(size, kinds_prefill, peaks, PREFILL_LEN, 1, PREFILL_LEN, False)}
             elif name == "rugedra":
@@ -736,7 +812,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--design", default=None, choices=["rugedra", "ravapel"],
+    ap.add_argument("--design", default=None, choices=["rugedra", "ravapel", "vofanex"],
                     help="instead of the default workload: this design at real layer sizes beside the closest "
                          "model the engine had, prompt and decode throughput and every kind of kernel")
     ap.add_argument("--sizes", default="w1024,w2048", help="with --design: which of " + ",".join(DESIGN_SIZES))

@@ -48,6 +48,9 @@ def random_model(config: dict[str, Any] | Any, seed: int = 0, dtype: str = "bflo
 def model_from_tensors(config: dict[str, Any], tensors: dict[str, Any], dtype: str, device,
                        max_positions: int | None = None) -> tuple[Model, Any]:
     cfg = config_from_dict(config)
+    complete = getattr(cfg, "with_tensor_shapes", None)
+    if complete is not None:  # (sizes that only a tensor's shape gives, as when a folder is read)
+        cfg = complete({n: tuple(t.shape) for n, t in tensors.items()})
     spec = build_model_spec(cfg)
     model = Model(spec, dtype, max_positions or spec.max_position_embeddings, device)
     expected = model.declared_weights()

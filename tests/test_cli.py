@@ -88,3 +88,36 @@ def test_generate_runs_a_ravapel_folder(tmp_path, capsys):
     for _ in range(6):
         ids.append(int(P.forward(cfg, weights, ids, torch.float64)[-1].argmax()))
     assert capsys.readouterr().out.split() == [str(t) for t in ids[len(prompt):]]
+
+
+def test_info_prints_a_vofanex_shape(tmp_path, capsys):
+    from tests import vofanex_configs as V
+
+    folder = H.write_model_dir(tmp_path / "m", V.MIXED, V.make_weights(V.MIXED, seed=2))
+    assert cli.main(["info", "--model", str(folder), "--gpu-mem", "180"]) == 0
+    out = capsys.readouterr().out
+    assert "architecture        Vofanex" in out and "layers / width      5 / 72" in out
+    assert "gla+dense, attention+moe, gla, attention+dense, gla+moe" in out
+    assert "attention windows   7, 10" in out and "state per request" in out
+
+
+@pytest.mark.gpu
+def test_generate_runs_a_vofanex_folder(tmp_path, capsys):
+    """`engine generate` on a Vofanex folder: the same entry point, scheduler and sampling as for the
+    other architectures; greedy tokens are the plain implementation's."""
+    import torch
+
+    from tests import plain_vofanex as P
+    from tests import vofanex_configs as V
+
+    cfg, weights = V.ODD, V.make_weights(V.ODD, seed=2)
+    folder = H.write_model_dir(tmp_path / "m", cfg, weights)
+    prompt = [5, 17, 3, 44, 9, 21, 30]
+    rc = cli.main(["generate", "--model", str(folder), "--prompt-ids", ",".join(map(str, prompt)), "--temperature", "0",
+                   "--max-tokens", "6", "--dtype", "float32", "--num-blocks", "16", "--block-size", "8",
+                   "--max-num-seqs", "2", "--max-num-batched-tokens", "4"])
+    assert rc == 0
+    ids = list(prompt)
+    for _ in range(6):
+        ids.append(int(P.forward(cfg, weights, ids, torch.float64)[-1].argmax()))
+    assert capsys.readouterr().out.split() == [str(t) for t in ids[len(prompt):]]

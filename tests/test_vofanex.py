@@ -389,3 +389,288 @@ def test_sink_attention_on_the_tensor_cores(d, dv, window):
     assert ops.launch_counts.get("sink_attention_mma", 0) == before + 5  # (the kernel under test did run)
     # (weights keep 16 bits of mantissa in the second product; outputs are rounded to bfloat16)
     torch.testing.assert_close(torch.cat(got), want, atol=0.015, rtol=0.01)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("heads,dim,vdim,rank,tau", [(3, 12, 20, 5, 8.0), (1, 5, 3, 1, 1.0), (2, 48, 16, 16, 16.0),
+                                                     (2, 100, 40, 7, 2.5), (1, 130, 8, 300, 4.0), (1, 260, 33, 3, 64.0)])
+def test_gated_linear_attention_in_pieces(device, heads, dim, vdim, rank, tau):
+    """The decay from its low-rank map and the recurrence over 61 tokens cut into pieces of 1 to 17
+    tokens, from and to a state slot, against the whole-sequence functions; the first token leaves
+    a mark that slow decays keep, so a state that is lost or starts anywhere but at zero shows; a
+    second request beside it must not disturb it."""
+    ops, g = _ops(device), torch.Generator().manual_seed(dim)
+    T, D = 61, torch.float64
+    q = torch.randn(T, heads, dim, generator=g)
+    k = torch.randn(T, heads, dim, generator=g)
+    v = torch.randn(T, heads, vdim, generator=g)
+    k[0], v[0] = 3.0, 5.0  # (the first token's mark)
+    y = torch.randn(T, rank, generator=g)
+    w2 = torch.randn(heads * dim, rank, generator=g) / rank ** 0.5
+    bias = torch.randn(heads * dim, generator=g) + 3.0
+    alpha = torch.sigmoid(y.to(D) @ w2.to(D).T + bias.to(D)).pow(1.0 / tau).view(T, heads, dim)
+    want = P.gla_recurrence(q.to(D) * dim ** -0.5, k.to(D), v.to(D), alpha).float()
+    forgot = P.gla_recurrence(q[1:].to(D) * dim ** -0.5, k[1:].to(D), v[1:].to(D), alpha[1:]).float()
+    assert (want[-1] - forgot[-1]).abs().max() > 1e-2  # (the last token still feels the first)
+    state = torch.zeros(3, heads * vdim * dim, device=device)
+    state[1] = 7.0  # another request's slot: left alone
+    got, decays, at = [], [], 0
+    for n in [1, 17, 2, 8, 1, 1, 16, 9, 6]:
+        # the request (slot 2) beside a stranger (slot 0) that brings 3 tokens of noise
+        ctx = _ctx([3, n], [0, at], device, slots=[0, 2])
+        rows = lambda x, w: torch.cat([torch.randn(3, w, generator=g), x[at: at + n].reshape(n, -1)]).to(device)  # noqa: E731
+        # the low-rank input sits in the last columns of a wider buffer, as in the mixer
+        wide = torch.cat([torch.zeros(3 + n, 2, device=device), rows(y, rank)], dim=1)
+        decay = torch.zeros(3 + n, heads * dim, device=device)
+        ops.lowrank_decay(wide[:, 2:], w2.to(device), bias.to(device), tau, decay)
+        out = torch.zeros(3 + n, heads * vdim, device=device)
+        ops.gated_recurrence(rows(q, heads * dim), decay, rows(k, heads * dim), None, rows(v, heads * vdim), state,
+                             ctx.slots, ctx, out, heads, dim, vdim, vdim, dim ** -0.5)
+        got.append(out[3:].cpu().view(n, heads, vdim))
+        decays.append(decay[3:].cpu().view(n, heads, dim))
+        at += n
+    torch.testing.assert_close(torch.cat(decays), alpha.float(), atol=2e-6, rtol=2e-6)
+    torch.testing.assert_close(torch.cat(got), want, atol=3e-4, rtol=3e-4)
+    assert torch.all(state[1] == 7.0)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("heads,vdim", [(3, 20), (1, 3), (5, 64), (2, 200)])
+def test_read_out_norm_with_a_silu_gate(device, heads, vdim):
+    ops, g = _ops(device), torch.Generator().manual_seed(vdim)
+    n, eps, D = 9, 1e-5, torch.float64
+    o = torch.randn(n, heads, vdim, generator=g) * 4
+    w = torch.randn(vdim, generator=g) + 1  # one weight for every head
+    pre = torch.randn(n, heads * vdim, generator=g) * 2
+    want = (P.rms(o.to(D), eps) * w.to(D)).reshape(n, -1) * (pre.to(D) * torch.sigmoid(pre.to(D)))
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
+        out = torch.zeros(n, heads * vdim, device=device, dtype=dtype)
+        wide = torch.cat([torch.zeros(n, 5), pre], dim=1).to(device)  # (the gate is a view of a wider buffer)
+        ops.recurrence_readout(o.reshape(n, -1).to(device), None, w.to(device), eps, wide[:, 5:], out, heads, vdim,
+                               vdim, gate_act="silu")
+        torch.testing.assert_close(out.float().cpu(), want.float(), atol=tol, rtol=tol)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("inter", [1, 24, 30, 1096, 5000])
+def test_polynorm_activation(device, inter):
+    """a N(z) + b N(z^2) + c N(z^3) + e with each power divided by its own root mean square; rows of
+    very different sizes, so that a norm shared between the powers or taken over the batch shows."""
+    ops, g = _ops(device), torch.Generator().manual_seed(inter)
+    n, eps, D = 6, 1e-5, torch.float64
+    z = torch.randn(n, inter, generator=g) * torch.tensor([0.01, 0.3, 1.0, 3.0, 10.0, 1e-4])[:, None]
+    coeff = torch.tensor([0.8, -0.6, 0.45, 0.1])
+    want = P.polynorm(z.to(D), coeff.to(D), eps).float()
+    out = torch.zeros(n, inter, device=device)
+    ops.polynorm(z.to(device), coeff.to(device), eps, out)
+    torch.testing.assert_close(out.cpu(), want, atol=2e-5, rtol=2e-5)
+    out16 = torch.zeros(n, inter, device=device, dtype=torch.bfloat16)
+    ops.polynorm(z.to(device), coeff.to(device), eps, out16)
+    torch.testing.assert_close(out16.float().cpu(), want, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("hidden", [50, 72, 1100])
+def test_gated_add_and_norm_in_one_kernel(device, hidden):
+    """h += sigmoid(W h' + b) * delta and the next norm of h, with the delta whole or in two partial
+    sums, with and without a bias, for all rows or for chosen ones (then h stays as it is), and
+    without a following norm."""
+    ops, g = _ops(device), torch.Generator().manual_seed(hidden)
+    n, eps, D = 7, 1e-5, torch.float64
+    h, delta = torch.randn(n, hidden, generator=g), torch.randn(2, n, hidden, generator=g) * 3
+    pre, bias, w = torch.randn(n, hidden, generator=g) * 2, torch.randn(hidden, generator=g), torch.randn(hidden, generator=g)
+    for b in (bias, None):
+        gate = torch.sigmoid(pre.to(D) + (0 if b is None else b.to(D)))
+        dev_b = None if b is None else b.to(device)
+        for parts in (delta, delta[0]):
+            whole = parts.to(D).sum(0) if parts.dim() == 3 else parts.to(D)
+            h_want = h.to(D) + gate * whole
+            out_want = P.rms(h_want, eps) * w.to(D)
+            hd, out = h.clone().to(device), torch.zeros(n, hidden, device=device)
+            ops.gated_add_norm(hd, parts.to(device), pre.to(device), dev_b, w.to(device), eps, out)
+            torch.testing.assert_close(hd.cpu(), h_want.float(), atol=1e-5, rtol=1e-5)
+            torch.testing.assert_close(out.cpu(), out_want.float(), atol=1e-5, rtol=1e-5)
+            rows = torch.tensor([5, 0], dtype=torch.int32, device=device)
+            hd2, out2 = h.clone().to(device), torch.zeros(2, hidden, device=device)
+            ops.gated_add_norm(hd2, parts.to(device), pre.to(device), dev_b, w.to(device), eps, out2, rows)
+            torch.testing.assert_close(out2.cpu(), out_want.float()[[5, 0]], atol=1e-5, rtol=1e-5)
+            assert torch.equal(hd2.cpu(), h)
+            hd3 = h.clone().to(device)
+            ops.gated_add_norm(hd3, parts.to(device), pre.to(device), dev_b, None, 0.0, None)
+            torch.testing.assert_close(hd3.cpu(), h_want.float(), atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("experts,top", [(8, 3), (5, 1), (3, 3), (2, 1), (7, 6), (64, 8)])
+def test_router_with_a_bias_weighs_only_the_chosen(device, experts, top):
+    """The bias decides who is chosen (it is as large as the logits), and the weights are the
+    softmax over the chosen logits alone."""
+    ops, g = _ops(device), torch.Generator().manual_seed(experts)
+    n, hidden, D = 33, 40, torch.float64
+    x = torch.randn(n, hidden, generator=g)
+    W = {"r.router": torch.randn(experts, hidden, generator=g) / hidden ** 0.5 * 2,
+         "r.router.b": torch.randn(experts, generator=g) * 2}
+    ids_want, w_want = P.route(x.to(D), {k: t.to(D) for k, t in W.items()}, "r", top)
+    no_bias = P.route(x.to(D), {"r.router": W["r.router"].to(D), "r.router.b": torch.zeros(experts, dtype=D)}, "r", top)[0]
+    if top < experts:
+        assert not torch.equal(ids_want.sort(-1).values, no_bias.sort(-1).values)
+    ids = torch.zeros(n, top, dtype=torch.int32, device=device)
+    weights = torch.zeros(n, top, device=device)
+    ops.route_topk(x.to(device), W["r.router"].to(device), 1, 1, ids, weights, bias=W["r.router.b"].to(device))
+    got = torch.zeros(n, experts).scatter_(1, ids.long().cpu(), weights.cpu())
+    want = torch.zeros(n, experts, dtype=D).scatter_(1, ids_want, w_want).float()
+    torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(weights.sum(-1).cpu(), torch.ones(n), atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_biases_unit_values_and_cache_rows(device):
+    """Queries, keys and values take their biases; each value head is divided by its root mean square
+    before it is cached; nothing is rotated; rows land where the slot mapping says."""
+    ops, g = _ops(device), torch.Generator().manual_seed(8)
+    n, H, G, d, dv, ps, eps, D = 9, 3, 2, 10, 14, 4, 1e-5, torch.float64
+    size = (H + G) * d + G * dv
+    proj = torch.randn(n, size + H, generator=g)  # (the head gates' columns follow and are left alone)
+    bias = torch.randn(size, generator=g)
+    pos = torch.tensor([0, 1, 2, 3, 17, 18, 19, 5, 6])
+    full = proj[:, :size].to(D) + bias.to(D)
+    q = full[:, : H * d]
+    k = full[:, H * d: (H + G) * d].view(n, G, d)
+    v = P.rms(full[:, (H + G) * d:].view(n, G, dv), eps)
+    q_out = torch.zeros(n, H * d, device=device)
+    kc, vc = torch.zeros(9, G, ps, d, device=device), torch.zeros(9, G, ps, dv, device=device)
+    slots = torch.tensor([p + 8 for p in pos.tolist()], dtype=torch.int32, device=device)  # pages 2..6
+    ops.qk_norm_rope_write(proj.to(device), pos.to(torch.int32).to(device), None, 0, None, None, eps, q_out, kc, vc,
+                           slots, H, G, d, dv, ps, bias=bias.to(device), value_norm=True)
+    torch.testing.assert_close(q_out.cpu(), q.float(), atol=1e-6, rtol=1e-6)
+    for i, s in enumerate(slots.tolist()):
+        torch.testing.assert_close(kc[s // ps, :, s % ps].cpu(), k[i].float(), atol=1e-6, rtol=1e-6)
+        torch.testing.assert_close(vc[s // ps, :, s % ps].cpu(), v[i].float(), atol=1e-5, rtol=1e-5)
+        torch.testing.assert_close(vc[s // ps, :, s % ps].cpu().pow(2).mean(-1), torch.ones(G), atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_embedding_rows_times_the_scale(device):
+    ops, g = _ops(device), torch.Generator().manual_seed(2)
+    table = torch.randn(23, 50, generator=g)
+    ids = torch.tensor([0, 22, 7, 7, 13], dtype=torch.int32)
+    for dtype in (torch.float32, torch.bfloat16):
+        t = table.to(dtype)
+        out = torch.zeros(5, 50, device=device)
+        ops.embedding(t.to(device), ids.to(device), out, 1.7)
+        want = P.embed(ids.tolist(), {"embed": t.double()}, {"embedding": {"scale": 1.7}}).float()
+        torch.testing.assert_close(out.cpu(), want, atol=1e-6, rtol=1e-6)
+
+
+# --- long decoding and generation through the engine ------------------------------------------------
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_through_state_and_pages(tmp_path, dtype):
+    """400 tokens decoded one by one after a short prompt, across many windows and pages: the
+    recurrent states and the cached rows carry what they must, and pages behind the windows go back
+    (the pool is smaller than the sequence)."""
+    from inference_engine_b200.kernels import get_ops
+
+    cfg = V.MIXED
+    weights = V.make_weights(cfg, seed=3)
+    toks = _requests(cfg, [410], seed=5)["r0"]
+    want = P.forward(cfg, weights, toks, torch.float64).float()
+    session = _session(tmp_path, cfg, weights, dtype, "cuda", get_ops("cuda"), 448, 16)
+    got = H.collect(session, H.trace_decode_tail({"a": toks}, 400))["a"]
+    H.assert_close(got, want, LABEL[dtype], "long decoding", _bound(tmp_path, dtype, cfg, weights, {"a": toks}, {"a": want}))
+
+
+def _greedy_plain(cfg, weights, prompt, count):
+    ids = list(prompt)
+    for _ in range(count):
+        ids.append(int(P.forward(cfg, weights, ids, torch.float64)[-1].argmax()))
+    return ids[len(prompt):]
+
+
+def _generate(cfg, weights, device, **kw):
+    from inference_engine_b200 import SamplingParams
+    from inference_engine_b200.engine.llm_engine import LLMEngine
+    from inference_engine_b200.engine.loading import model_from_tensors
+
+    model, _ = model_from_tensors(cfg, weights, "float32", device, 128)
+    engine = LLMEngine(model, None, (), num_blocks=48, block_size=8, max_num_seqs=3,
+                       max_num_batched_tokens=16, debug_checks=True, **kw)
+    prompts = {f"p{i}": _requests(cfg, [n], seed=90 + i)["r0"] for i, n in enumerate([5, 40, 23, 1, 31])}
+    for rid, prompt in prompts.items():
+        engine.add_request(rid, prompt, SamplingParams(max_tokens=10, temperature=0.0))
+    got: dict[str, list[int]] = {rid: [] for rid in prompts}
+    while engine.has_unfinished():
+        for out in engine.step():
+            got[out.request_id].append(out.token_id)
+    engine.cache.check_invariants()
+    assert engine.cache.slots.num_free == engine.cache.slots.num_slots
+    return engine, prompts, got
+
+
+def test_greedy_generation_on_the_plain_kernels():
+    """The engine's own entry point and scheduler on the CPU stand-ins of the kernels."""
+    from tests.ref_ops import RefOps
+
+    cfg = V.ATTENTION_FIRST
+    weights = V.make_weights(cfg, seed=4)
+    _, prompts, got = _generate(cfg, weights, "cpu", ops=RefOps())
+    for rid, prompt in prompts.items():
+        assert got[rid] == _greedy_plain(cfg, weights, prompt, 10), rid
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["mixed", "odd"])
+def test_greedy_generation_through_the_engine(name):
+    """`LLMEngine` with the scheduler cutting prompts into portions and batching requests (three at
+    a time, so state slots and pages serve one request after another), decode steps captured and
+    launched ahead: the tokens are the plain implementation's greedy choices."""
+    cfg = V.CONFIGS[name]
+    weights = V.make_weights(cfg, seed=4)
+    engine, prompts, got = _generate(cfg, weights, "cuda")
+    assert engine.graphs is not None  # decode steps are captured, with per-request state too
+    for rid, prompt in prompts.items():
+        assert got[rid] == _greedy_plain(cfg, weights, prompt, 10), rid
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_captured_short_steps_with_portions(tmp_path, dtype):
+    """Portions and mixed batches replayed through captured launch sequences (launched for bounds,
+    padded with tokens that belong to no request): key and value sizes the tensor-core attention
+    takes, so in bfloat16 that kernel runs sized by the token bound.  Against the plain
+    implementation; in 32-bit equal bit for bit to the eagerly launched steps."""
+    from inference_engine_b200.engine.graphs import DecodeGraphs, MixedGraphs
+    from inference_engine_b200.kernels import get_ops
+
+    cfg = V.config(64, 89, [
+        (V.gla(2, 16, 24, tau=6.0), V.dense(48)),
+        (V.attention(4, 2, 16, 32, window=24), V.moe(4, 2, 24)),
+        (V.attention(2, 1, 32, 16, window=9), None),
+        (V.gla(3, 8, 8, tau=2.0), V.dense(40)),
+    ])
+    weights = V.make_weights(cfg, seed=6, ranks={0: 4, 3: 6})
+    requests = _requests(cfg, [70, 45, 33, 90, 20, 60], seed=300)
+    want = _want(cfg, weights, requests)
+    tol = _bound(tmp_path, dtype, cfg, weights, requests, want)
+    mixed, peak = H.trace_mixed(requests, seed=2, tail=6, max_portion=20)
+    results = {}
+    for captured in (True, False):
+        for mode, (trace, room) in {"portions": (H.trace_portions(requests), 128), "mixed": (mixed, peak)}.items():
+            session = _session(tmp_path / f"{mode}{captured}", cfg, weights, dtype, "cuda", get_ops("cuda"), room, 8)
+            if captured:
+                graphs = MixedGraphs(DecodeGraphs(session.runner, 256, max(64, -(-room // 8))))
+                eager = session.runner.step
+                session.runner.step = lambda entries, g=graphs, e=eager: g.run(entries) if g.can_run(entries) else e(entries)
+            got = H.collect(session, trace)
+            for rid in requests:
+                H.assert_close(got[rid], want[rid], LABEL[dtype], f"captured={captured} {mode} {rid}", tol)
+            if captured:
+                assert graphs.replays > len(requests)
+            results[(captured, mode)] = got
+    if dtype == "float32":
+        for mode in ("portions", "mixed"):
+            for rid in requests:
+                assert torch.equal(results[(True, mode)][rid], results[(False, mode)][rid]), (mode, rid)
+    get_ops("cuda").check_errors()
