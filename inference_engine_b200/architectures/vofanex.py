@@ -53,7 +53,9 @@ def _parse_mixer(kind: str, raw: dict, where: str) -> dict:
             raise ConfigError(f"config.json: {where}.tau must be a positive number")
         out["decay_rank"] = int(raw["decay_rank"]) if raw.get("decay_rank") is not None else None
     else:
-        out = {k: _need(raw, k, int, where) for k in ("heads", "kv_heads", "dim", "vdim")}
+        out = {k: _need(raw, k, int, where) for k in ("heads", "dim", "vdim")}
+        # (a mixer that does not share keys and values among heads need not say so)
+        out["kv_heads"] = _need(raw, "kv_heads", int, where) if raw.get("kv_heads") is not None else out["heads"]
         out["scale"] = _need(raw, "scale", float, where)
         if out["kv_heads"] < 1 or out["heads"] % out["kv_heads"]:
             raise ConfigError(f"config.json: {where}.heads is not a multiple of kv_heads")

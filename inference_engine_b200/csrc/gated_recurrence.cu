@@ -15,8 +15,8 @@
 //    numbers), taken as exp(logsigmoid(z_t) / tau); w_t = k_t, u_t = v_t; the read-out's gate is
 //    silu(.) instead of sigmoid(.).
 //
-// Kernels: lowrank_decay (a block takes eight tokens and 128 channels, so that a row of W2 is read
-// once per eight tokens); short_conv_residual (+ tail update): out = x + causal convolution of x over time per
+// Kernels: lowrank_decay (a block takes sixteen tokens and 128 channels, so that a row of W2 is read
+// once per sixteen tokens); short_conv_residual (+ tail update): out = x + causal convolution of x over time per
 // channel, the last taps - 1 inputs kept per request; hgrn2_gates; mlstm_gates (a warp per request
 // and head walks the step's tokens in order); gated_recurrence (columns of S do not interact: a
 // block owns some columns of one head of one request, TPC lanes a column, tokens in order, eight at
@@ -153,32 +153,43 @@ mlstm_gates_kernel(const float* __restrict__ gi, const float* __restrict__ gf, i
 
 // grid: (blocks of LD_TOKENS tokens, blocks of 128 channels).  y: element (n, r) at [n * y_ld + r]; w2: [channels, rank];
 // decay: [N, channels] = exp(logsigmoid(w2 y + bias) * inv_tau).  A channel's sum runs over r in rising order.
-constexpr int LD_TOKENS = 8;
+// The block's 128 rows of w2 and its tokens' inputs pass through shared memory 32 ranks at a time: a warp
+// reads 32 consecutive numbers of a row at once, and rows sit 33 words apart so that the threads of a
+// warp, one channel each, read different banks.
+constexpr int LD_TOKENS = 16, LD_RANKS = 32;
 __global__ void __launch_bounds__(128)
 lowrank_decay_kernel(const float* __restrict__ y, int y_ld, const float* __restrict__ w2,
                      const float* __restrict__ bias, float inv_tau, float* __restrict__ decay, int num_tokens,
                      int channels, int rank) {
-    extern __shared__ float ys[];  // [LD_TOKENS][rank]
+    __shared__ float ws[128 * (LD_RANKS + 1)];
+    __shared__ float ys[LD_TOKENS * LD_RANKS];
     ie_pdl_trigger();
     ie_pdl_wait();
-    int n0 = blockIdx.x * LD_TOKENS;
+    int n0 = blockIdx.x * LD_TOKENS, c0 = blockIdx.y * 128;
     int cnt = min(LD_TOKENS, num_tokens - n0);
-    for (int i = threadIdx.x; i < LD_TOKENS * rank; i += 128) {
-        int t = i / rank, r = i - t * rank;
-        ys[i] = t < cnt ? y[(size_t)(n0 + t) * y_ld + r] : 0.f;
-    }
-    __syncthreads();
-    int c = blockIdx.y * 128 + threadIdx.x;
-    if (c >= channels) return;
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float acc[LD_TOKENS];
 #pragma unroll
     for (int t = 0; t < LD_TOKENS; ++t) acc[t] = 0.f;
-    const float* wrow = w2 + (size_t)c * rank;
-    for (int r = 0; r < rank; ++r) {
-        float wv = wrow[r];
+    for (int r0 = 0; r0 < rank; r0 += LD_RANKS) {
+        int width = min(LD_RANKS, rank - r0);
+        if (r0 > 0) __syncthreads();  // everyone is done with the last piece
+        for (int row = warp; row < 128; row += 4) {
+            int c = c0 + row;
+            ws[row * (LD_RANKS + 1) + lane] = (c < channels && lane < width) ? w2[(size_t)c * rank + r0 + lane] : 0.f;
+        }
+        for (int t = warp; t < LD_TOKENS; t += 4)
+            ys[t * LD_RANKS + lane] = (t < cnt && lane < width) ? y[(size_t)(n0 + t) * y_ld + r0 + lane] : 0.f;
+        __syncthreads();
+        const float* wrow = ws + threadIdx.x * (LD_RANKS + 1);
+        for (int r = 0; r < width; ++r) {
+            float wv = wrow[r];
 #pragma unroll
-        for (int t = 0; t < LD_TOKENS; ++t) acc[t] = fmaf(wv, ys[t * rank + r], acc[t]);
+            for (int t = 0; t < LD_TOKENS; ++t) acc[t] = fmaf(wv, ys[t * LD_RANKS + r], acc[t]);
+        }
     }
+    int c = c0 + threadIdx.x;
+    if (c >= channels) return;
     float b = bias != nullptr ? bias[c] : 0.f;
 #pragma unroll
     for (int t = 0; t < LD_TOKENS; ++t)
@@ -427,10 +438,9 @@ IE_API int ie_short_conv_residual(const void* x, int dtype, const float* w, floa
 IE_API int ie_lowrank_decay(const float* y, int y_ld, const float* w2, const float* bias, float inv_tau,
                             float* decay, int num_tokens, int channels, int rank, void* stream) {
     if (num_tokens <= 0 || channels <= 0) return 0;
-    size_t smem = (size_t)LD_TOKENS * rank * sizeof(float);
-    if (rank < 1 || smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    if (rank < 1) return (int)cudaErrorInvalidValue;
     dim3 grid((num_tokens + LD_TOKENS - 1) / LD_TOKENS, (channels + 127) / 128);
-    return ie_launch(lowrank_decay_kernel, grid, dim3(128), smem, (cudaStream_t)stream, y, y_ld, w2, bias, inv_tau,
+    return ie_launch(lowrank_decay_kernel, grid, dim3(128), 0, (cudaStream_t)stream, y, y_ld, w2, bias, inv_tau,
                      decay, num_tokens, channels, rank);
 }
 

@@ -14,6 +14,14 @@
 // value and the remainder), so it keeps 16 bits of mantissa; O stays in registers and is rescaled when
 // a row's maximum grows.  A row's result depends on its own request alone (tiles are aligned to
 // position 0, keys are added in rising order).
+//
+// Steps whose requests bring few tokens each (decoding) and whose window is known cut the key tiles
+// of a request and head among several blocks (`splits` ranges of `tiles_per_split` tiles, counted from
+// the first tile the request's first row sees, so the cut depends on the request's own positions
+// alone): each block leaves its unnormalised sums, its running maximum and its running sum in a
+// 32-bit scratch row, and a second kernel merges the ranges in rising order, adds the sink's term
+// and applies the gate.  Such a block serves all query heads of one key/value head at once: its rows
+// are (token, head of the group), so a key tile is brought once for the group.
 #include "common.cuh"
 #include <math.h>
 
@@ -72,22 +80,31 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
                           int table_width, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
                           __nv_bfloat16* __restrict__ out, int heads, int kv_heads, int page_size,
                           int total_pages, float scale, int window, const float* __restrict__ sinks,
-                          const float* __restrict__ out_gate, int gate_ld, int* err) {
+                          const float* __restrict__ out_gate, int gate_ld, float* __restrict__ partial,
+                          int splits, int tiles_per_split, int* err) {
     extern __shared__ __align__(16) unsigned char raw[];
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(raw);  // [ROWS][LDK]
     __nv_bfloat16* ks = qs + ROWS * LDK;                        // [2][KEYS][LDK]
     __nv_bfloat16* vs = ks + 2 * KEYS * LDK;                    // [2][KEYS][LDV]
     ie_pdl_trigger();
     ie_pdl_wait();
-    int seq = blockIdx.z, head = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
+    // (with `partial` the first grid dimension counts ranges of key tiles and the second key/value heads;
+    // row r of the block is then token r / group with query head kvh * group + r % group)
+    const bool split_mode = partial != nullptr;
+    const int group = heads / kv_heads;
+    int seq = blockIdx.z, head = blockIdx.y, tile = split_mode ? 0 : gridDim.x - 1 - blockIdx.x;
     int q0 = cu_q[seq], q_len = cu_q[seq + 1] - q0;
     int row0 = tile * ROWS;
     if (row0 >= q_len) return;
-    int rows_here = min(ROWS, q_len - row0);
+    int tokens_here = min(ROWS, q_len - row0);
+    int rows_here = split_mode ? q_len * group : tokens_here;
     int start = ctx_lens[seq] - q_len;  // position of the request's first token of this step
-    int first_pos = start + row0, last_pos = first_pos + rows_here - 1;
+    int first_pos = start + row0, last_pos = first_pos + tokens_here - 1;
     int lo_min = window > 0 ? max(first_pos - window + 1, 0) : 0;
-    int kvh = head / (heads / kv_heads);
+    int kvh = split_mode ? head : head / group;
+    // a row's token (counted from the block's first) and query head
+    auto row_token = [&](int r) { return split_mode ? r / group : r; };
+    auto row_head = [&](int r) { return split_mode ? kvh * group + r % group : head; };
     int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int* table = block_tables + (size_t)seq * table_width;
     int page_shift = 31 - __clz(page_size);
@@ -121,13 +138,25 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     int t_begin = lo_min / KEYS, t_end = last_pos / KEYS;  // inclusive
+    if (split_mode) {
+        t_begin += blockIdx.x * tiles_per_split;
+        t_end = min(t_end, t_begin + tiles_per_split - 1);
+        if (t_begin > t_end) {  // nothing in this range: a maximum of -inf tells the merge to pass over it
+            if (tid < rows_here) {
+                float* dst = partial + (((size_t)(q0 + row_token(tid)) * heads + row_head(tid)) * splits + blockIdx.x) * (DV + 2);
+                dst[DV] = -INFINITY;
+                dst[DV + 1] = 0.f;
+            }
+            return;
+        }
+    }
     load_tile(t_begin, 0);
     // the block's queries (rows beyond the request's tokens read as zero)
     for (int i = tid; i < ROWS * (D / 8); i += THREADS) {
         int r = i / (D / 8), c = i - r * (D / 8);
         uint4 val = make_uint4(0u, 0u, 0u, 0u);
         if (r < rows_here)
-            val = *reinterpret_cast<const uint4*>(q + ((size_t)(q0 + row0 + r) * heads + head) * D + c * 8);
+            val = *reinterpret_cast<const uint4*>(q + ((size_t)(q0 + row0 + row_token(r)) * heads + row_head(r)) * D + c * 8);
         *reinterpret_cast<uint4*>(qs + r * LDK + c * 8) = val;
     }
     __syncthreads();
@@ -141,15 +170,16 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
     for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     // the two rows of this thread: positions and the first position each may see
     int r_a = warp * 16 + g, r_b = r_a + 8;
-    int pos_a = r_a < rows_here ? first_pos + r_a : -1, pos_b = r_b < rows_here ? first_pos + r_b : -1;
+    int pos_a = r_a < rows_here ? first_pos + row_token(r_a) : -1, pos_b = r_b < rows_here ? first_pos + row_token(r_b) : -1;
     int lo_a = window > 0 ? max(pos_a - window + 1, 0) : 0;
     int lo_b = window > 0 ? max(pos_b - window + 1, 0) : 0;
     // running maximum (of score * scale * log2 e) and this thread's share of the running sum; the
     // sink's term of the sum is counted by the first thread of the four that share a row
     const float sl2 = scale * LOG2E;
-    float sink2 = sinks != nullptr ? sinks[head] * LOG2E : -INFINITY;
+    const bool with_sink = sinks != nullptr && !split_mode;  // (split: the merge adds the sink's term)
+    float sink2 = with_sink ? sinks[head] * LOG2E : -INFINITY;
     float m_a = sink2, m_b = sink2;
-    float l_a = (sinks != nullptr && t4 == 0) ? 1.f : 0.f, l_b = l_a;
+    float l_a = (with_sink && t4 == 0) ? 1.f : 0.f, l_b = l_a;
 
     int buf = 0;
     for (int t = t_begin; t <= t_end; ++t, buf ^= 1) {
@@ -234,6 +264,21 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
     if (!active) return;
     l_a = quad_sum(l_a);
     l_b = quad_sum(l_b);
+    if (split_mode) {
+        float* dst_a = partial + (((size_t)(q0 + row_token(r_a)) * heads + row_head(r_a)) * splits + blockIdx.x) * (DV + 2);
+        float* dst_b = partial + (((size_t)(q0 + row_token(r_b)) * heads + row_head(r_b)) * splits + blockIdx.x) * (DV + 2);
+#pragma unroll
+        for (int nt = 0; nt < DV / 8; ++nt) {
+            int c = nt * 8 + t4 * 2;
+            if (pos_a >= 0) *reinterpret_cast<float2*>(dst_a + c) = make_float2(o[nt][0], o[nt][1]);
+            if (pos_b >= 0) *reinterpret_cast<float2*>(dst_b + c) = make_float2(o[nt][2], o[nt][3]);
+        }
+        if (t4 == 0) {
+            if (pos_a >= 0) { dst_a[DV] = m_a; dst_a[DV + 1] = l_a; }
+            if (pos_b >= 0) { dst_b[DV] = m_b; dst_b[DV + 1] = l_b; }
+        }
+        return;
+    }
     float f_a = l_a > 0.f ? 1.0f / l_a : 0.f, f_b = l_b > 0.f ? 1.0f / l_b : 0.f;
     if (out_gate != nullptr) {
         if (pos_a >= 0) f_a *= 1.0f / (1.0f + expf(-out_gate[(size_t)(q0 + row0 + r_a) * gate_ld + head]));
@@ -248,6 +293,45 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
         if (pos_b >= 0) *reinterpret_cast<unsigned*>(out_b + c) = pack_bf16(o[nt][2] * f_b, o[nt][3] * f_b);
     }
 }
+
+// grid: tokens * heads.  Merges a token and head's ranges in rising order: maxima and sums are in units
+// of log2 e; the sink (if any) is one more term of the sum; the gate multiplies the result.
+__global__ void __launch_bounds__(128)
+sink_attention_merge_kernel(const float* __restrict__ partial, const int* __restrict__ cu_q, int num_seqs,
+                            __nv_bfloat16* __restrict__ out, int heads, int splits,
+                            const float* __restrict__ sinks, const float* __restrict__ out_gate, int gate_ld) {
+    ie_pdl_trigger();
+    ie_pdl_wait();
+    int token = blockIdx.x / heads, head = blockIdx.x - token * heads;
+    if (token >= cu_q[num_seqs]) return;  // (a captured step's padding belongs to no request)
+    const float* src = partial + ((size_t)token * heads + head) * splits * (DV + 2);
+    float m = sinks != nullptr ? sinks[head] * LOG2E : -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, src[(size_t)s * (DV + 2) + DV]);
+    float l = sinks != nullptr ? exp2f(sinks[head] * LOG2E - m) : 0.f;
+    if (m == -INFINITY) m = 0.f;
+    float acc[(DV + 127) / 128];
+#pragma unroll
+    for (int i = 0; i < (DV + 127) / 128; ++i) acc[i] = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float* row = src + (size_t)s * (DV + 2);
+        float ms = row[DV];
+        if (ms == -INFINITY) continue;  // (an empty range: its sums were never written)
+        float w = exp2f(ms - m);
+        l += row[DV + 1] * w;
+#pragma unroll
+        for (int i = 0; i < (DV + 127) / 128; ++i) {
+            int c = i * 128 + threadIdx.x;
+            if (c < DV) acc[i] = fmaf(row[c], w, acc[i]);
+        }
+    }
+    float f = l > 0.f ? 1.0f / l : 0.f;
+    if (out_gate != nullptr) f *= 1.0f / (1.0f + expf(-out_gate[(size_t)token * gate_ld + head]));
+#pragma unroll
+    for (int i = 0; i < (DV + 127) / 128; ++i) {
+        int c = i * 128 + threadIdx.x;
+        if (c < DV) out[((size_t)token * heads + head) * DV + c] = __float2bfloat16_rn(acc[i] * f);
+    }
+}
 }  // namespace
 
 IE_API int ie_sink_attention_dims(int* d, int* dv) {
@@ -260,7 +344,8 @@ IE_API int ie_sink_attention_mma(const void* q, const void* k_cache, const void*
                                  int table_width, const int* cu_q, const int* ctx_lens, void* out, int num_seqs,
                                  int max_q_len, int heads, int kv_heads, int page_size, int total_pages,
                                  float scale, int window, const float* sinks, const float* out_gate, int gate_ld,
-                                 int* err, void* stream) {
+                                 float* partial, int splits, int tiles_per_split, int num_tokens, int* err,
+                                 void* stream) {
     if (num_seqs <= 0 || max_q_len <= 0) return 0;
     if (kv_heads <= 0 || heads % kv_heads != 0 || page_size < 1 || (page_size & (page_size - 1)) || window < 0)
         return (int)cudaErrorInvalidValue;
@@ -268,9 +353,24 @@ IE_API int ie_sink_attention_mma(const void* q, const void* k_cache, const void*
     static IePerDevice allowed;
     cudaError_t e = ie_allow_smem(allowed, sink_attention_mma_kernel, smem);
     if (e != cudaSuccess) return (int)e;
+    if (partial != nullptr) {
+        // ranges of key tiles: a request's tokens times the heads of a group are one tile of rows, and
+        // the scratch holds [num_tokens, heads, splits, DV + 2] floats
+        if (max_q_len * (heads / kv_heads) > ROWS || splits < 1 || tiles_per_split < 1 || num_tokens < 1)
+            return (int)cudaErrorInvalidValue;
+        int rc = ie_launch(sink_attention_mma_kernel, dim3(splits, kv_heads, num_seqs), dim3(THREADS), smem,
+                           (cudaStream_t)stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
+                           (const __nv_bfloat16*)v_cache, block_tables, table_width, cu_q, ctx_lens, (__nv_bfloat16*)out,
+                           heads, kv_heads, page_size, total_pages, scale, window, sinks, out_gate, gate_ld, partial,
+                           splits, tiles_per_split, err);
+        if (rc != 0) return rc;
+        return ie_launch(sink_attention_merge_kernel, dim3(num_tokens * heads), dim3(128), 0, (cudaStream_t)stream,
+                         (const float*)partial, cu_q, num_seqs, (__nv_bfloat16*)out, heads, splits, sinks, out_gate,
+                         gate_ld);
+    }
     dim3 grid((max_q_len + ROWS - 1) / ROWS, heads, num_seqs);
     return ie_launch(sink_attention_mma_kernel, grid, dim3(THREADS), smem, (cudaStream_t)stream,
                      (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_tables,
                      table_width, cu_q, ctx_lens, (__nv_bfloat16*)out, heads, kv_heads, page_size, total_pages, scale,
-                     window, sinks, out_gate, gate_ld, err);
+                     window, sinks, out_gate, gate_ld, (float*)nullptr, 1, 0, err);
 }

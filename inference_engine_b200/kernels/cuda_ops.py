@@ -1306,10 +1306,15 @@ class CudaOps:
             except OSError as exc:
                 raise KernelError(f"the kernel library {path} could not be loaded: {exc}") from exc
             P, I, F = c_void_p, c_int, c_float
-            lib.ie_sink_attention_mma.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P, I, P, P]
+            lib.ie_sink_attention_mma.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P, I, P, I, I, I,
+                                                  P, P]
             lib.ie_sink_attention_mma.restype = c_int
             self._sinkattn_libs[(hd, vdim)] = lib
         return lib
+
+    # requests that bring at most so many tokens have their window's keys cut among blocks, each of
+    # which serves the query heads of one key/value head (tokens x heads of a group: 64 rows at most)
+    SINK_SPLIT_ROWS = 8
 
     @_kind("attention.sink")
     def sink_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, vdim, page_size, scale,
@@ -1321,8 +1326,11 @@ class CudaOps:
         value sizes that are multiples of 16 up to 256 runs the tensor-core kernel (a block per 64
         positions of a request and head, for prompt portions and single tokens; lengths and tables
         are read on the device, and a captured step is launched for the most tokens a request can
-        bring within its bounds); 32-bit and other sizes the general kernel.  Neither kernel's
-        order of operations depends on the batch."""
+        bring within its bounds; when no request brings more than a few tokens and there is a
+        window, the window's key tiles are cut among blocks and merged by a second kernel, so a
+        decoded token's sums are the same numbers in another order than in a step that also holds
+        a prompt portion); 32-bit and other sizes the general kernel, whose order of operations
+        does not depend on the batch."""
         if gate is not None and (gate.dtype != self.torch.float32 or gate.stride(1) != 1):
             raise KernelError("sink_attention: the output gate must be a 32-bit view with unit stride")
         if (self.sink_mma and q.dtype == self.torch.bfloat16 and hd % 16 == 0 and vdim % 16 == 0
@@ -1330,12 +1338,21 @@ class CudaOps:
             lib = self._sink_attention_lib(hd, vdim)
             bounds = getattr(ctx, "bounds", None)
             longest = bounds[0] if bounds is not None else ctx.max_q_len  # (a captured step: its token bound)
+            scratch, splits, per_split = None, 1, 0
+            if window and longest <= self.SINK_SPLIT_ROWS and longest * (nh // nkv) <= 64:
+                # the tiles between the first row's oldest key and the last row's own position, in
+                # ranges of two: from the window and the row bound alone, so a captured launch stays valid
+                tiles = (int(window) + longest - 2) // 64 + 2
+                per_split = 2
+                splits = -(-tiles // per_split)
+                if splits > 1:
+                    scratch = self._scratch(ctx, "attn.sink_partial", ctx.num_tokens * nh * splits * (vdim + 2), q.device)
             self._check(lib.ie_sink_attention_mma(
                 q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
                 block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(), ctx.num_seqs,
                 longest, nh, nkv, page_size, k_cache.shape[0], scale, int(window or 0), self._ptr(sinks),
-                self._ptr(gate), 0 if gate is None else gate.stride(0), self._err_ptr, self._stream()),
-                "sink_attention_mma")
+                self._ptr(gate), 0 if gate is None else gate.stride(0), self._ptr(scratch), splits, per_split,
+                ctx.num_tokens, self._err_ptr, self._stream()), "sink_attention_mma")
             return
         self._check(self._paged_attention_generic(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q),

@@ -373,7 +373,8 @@ def test_sink_attention_on_the_tensor_cores(d, dv, window):
     kc[pages + 3], vc[pages + 3] = 0.5, 0.25
     before = ops.launch_counts.get("sink_attention_mma", 0)
     got, at = [], 0
-    for n in [70, 33, 130, 1, 99]:
+    portions = [70, 33, 1, 2, 5, 130, 1, 8, 83]  # (few tokens: the window's key tiles are cut among blocks)
+    for n in portions:
         ctx = _ctx([n, 1], [at, 0], "cuda")
         qq = torch.cat([q[at: at + n].reshape(n, -1), torch.ones(1, H * d)]).to("cuda", torch.bfloat16)
         gg = torch.cat([gate[at: at + n], torch.zeros(1, H)]).cuda()
@@ -386,7 +387,7 @@ def test_sink_attention_on_the_tensor_cores(d, dv, window):
         torch.testing.assert_close(out[n].float().cpu().view(H, dv), lone.expand(H, dv), atol=2e-3, rtol=2e-2)
         at += n
     ops.check_errors()
-    assert ops.launch_counts.get("sink_attention_mma", 0) == before + 5  # (the kernel under test did run)
+    assert at == T and ops.launch_counts.get("sink_attention_mma", 0) == before + len(portions)  # (the kernel under test did run)
     # (weights keep 16 bits of mantissa in the second product; outputs are rounded to bfloat16)
     torch.testing.assert_close(torch.cat(got), want, atol=0.015, rtol=0.01)
 
