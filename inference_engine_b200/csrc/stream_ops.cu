@@ -174,14 +174,15 @@ sandwich_norm_kernel(float* __restrict__ h, const float* __restrict__ delta, int
 
 __device__ __forceinline__ float sigmoid_precise(float z) { return 1.0f / (1.0f + expf(-z)); }
 
-// gate_pre: [N, hidden] 32-bit (rows as in h); gate_bias: [hidden] or null.  `rows` selects rows and
+// gate_pre: [N, hidden] 32-bit (rows as in h), or `gate_partials` such arrays `gate_stride` apart, the parts
+// of a split product, added in order; gate_bias: [hidden] or null.  `rows` selects rows and
 // leaves h as it is; out == null: only h is brought up to date.
 template <typename OutT, int VEC>
 __global__ void __launch_bounds__(SN_THREADS)
 gated_add_norm_kernel(float* __restrict__ h, const float* __restrict__ delta, int num_partials, size_t partial_stride,
-                      const float* __restrict__ gate_pre, const float* __restrict__ gate_bias,
-                      const float* __restrict__ weight, float eps, OutT* __restrict__ out,
-                      const int* __restrict__ rows, int hidden) {
+                      const float* __restrict__ gate_pre, int gate_partials, size_t gate_stride,
+                      const float* __restrict__ gate_bias, const float* __restrict__ weight, float eps,
+                      OutT* __restrict__ out, const int* __restrict__ rows, int hidden) {
     extern __shared__ __align__(16) float row_buf[];  // [hidden]
     __shared__ float red[SN_THREADS / 32];
     ie_pdl_trigger();
@@ -197,6 +198,11 @@ gated_add_norm_kernel(float* __restrict__ h, const float* __restrict__ delta, in
             for (int v = 0; v < VEC; ++v) y.v[v] += d.v[v];
         }
         Pack<VEC> g = load_pack<VEC>(gate_pre + src + i), x = load_pack<VEC>(h + src + i);
+        for (int p = 1; p < gate_partials; ++p) {
+            Pack<VEC> d = load_pack<VEC>(gate_pre + p * gate_stride + src + i);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) g.v[v] += d.v[v];
+        }
         if (gate_bias != nullptr) {
             Pack<VEC> b = load_pack<VEC>(gate_bias + i);
 #pragma unroll
@@ -423,15 +429,17 @@ IE_API int ie_weighted_sum(const float* a, float sa, const float* b, float sb, f
 // `delta` is the sum of `num_partials` arrays; `out` may be null (only h is brought up to date);
 // `rows` selects rows, and then h is not modified.
 IE_API int ie_gated_add_norm(float* h, const float* delta, int num_partials, long long partial_stride,
-                             const float* gate_pre, const float* gate_bias, const float* weight, float eps,
+                             const float* gate_pre, int gate_partials, long long gate_stride,
+                             const float* gate_bias, const float* weight, float eps,
                              void* out, int out_dtype, const int* rows, int num_rows, int hidden, void* stream) {
     if (num_rows <= 0) return 0;
-    if (delta == nullptr || gate_pre == nullptr || num_partials < 1) return (int)cudaErrorInvalidValue;
+    if (delta == nullptr || gate_pre == nullptr || num_partials < 1 || gate_partials < 1)
+        return (int)cudaErrorInvalidValue;
     if (out != nullptr && weight == nullptr) return (int)cudaErrorInvalidValue;
     size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
-    bool vec = hidden % 4 == 0 && (size_t)partial_stride % 4 == 0 &&
+    bool vec = hidden % 4 == 0 && (size_t)partial_stride % 4 == 0 && (size_t)gate_stride % 4 == 0 &&
                ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(delta) |
                  reinterpret_cast<uintptr_t>(gate_pre) | reinterpret_cast<uintptr_t>(gate_bias) |
                  reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(out)) % 16 == 0);
@@ -443,8 +451,8 @@ IE_API int ie_gated_add_norm(float* h, const float* delta, int num_partials, lon
             if (e != cudaSuccess) return (int)e;                                                                   \
         }                                                                                                          \
         return ie_launch(gated_add_norm_kernel<T, V>, dim3(num_rows), dim3(SN_THREADS), smem, s, h, delta,         \
-                         num_partials, (size_t)partial_stride, gate_pre, gate_bias, weight, eps, (T*)out, rows,    \
-                         hidden);                                                                                  \
+                         num_partials, (size_t)partial_stride, gate_pre, gate_partials, (size_t)gate_stride,       \
+                         gate_bias, weight, eps, (T*)out, rows, hidden);                                           \
     } while (0)
     if (out_dtype == IE_BF16) {
         if (vec) IE_GN_LAUNCH(__nv_bfloat16, 4);

@@ -151,7 +151,9 @@ class GatedPreNormResidualBlock(Block):
     def _gate(self, which: str, x, ctx) -> ResidualGate:
         import torch
 
-        pre = ctx.ops.linear(x, self.w_gate[which], ws=ctx.ws, tag="resgate." + which, out_dtype=torch.float32)
+        # (the product may come back as partial sums: the kernel that applies the gate adds them)
+        pre = ctx.ops.linear(x, self.w_gate[which], ws=ctx.ws, tag="resgate." + which, out_dtype=torch.float32,
+                             allow_split=True)
         return ResidualGate(pre, self.gate_bias[which])
 
     @property

@@ -373,6 +373,8 @@ class RefOps:
     def gated_add_norm(self, h, delta, gate_pre, gate_bias, weight, eps, out, rows=None):
         if delta.dim() == 3:
             delta = delta.sum(0)
+        if gate_pre.dim() == 3:
+            gate_pre = gate_pre.sum(0)
         g = gate_pre if gate_bias is None else gate_pre + gate_bias
         if rows is None:
             h.add_(torch.sigmoid(g) * delta)

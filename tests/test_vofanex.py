@@ -499,6 +499,12 @@ def test_gated_add_and_norm_in_one_kernel(device, hidden):
             hd3 = h.clone().to(device)
             ops.gated_add_norm(hd3, parts.to(device), pre.to(device), dev_b, None, 0.0, None)
             torch.testing.assert_close(hd3.cpu(), h_want.float(), atol=1e-5, rtol=1e-5)
+            # the gate's product may arrive in parts too
+            halves = torch.stack([pre * 0.25, pre * 0.75]).to(device)
+            hd4, out4 = h.clone().to(device), torch.zeros(n, hidden, device=device)
+            ops.gated_add_norm(hd4, parts.to(device), halves, dev_b, w.to(device), eps, out4)
+            torch.testing.assert_close(hd4.cpu(), h_want.float(), atol=1e-5, rtol=1e-5)
+            torch.testing.assert_close(out4.cpu(), out_want.float(), atol=1e-5, rtol=1e-5)
 
 
 @pytest.mark.parametrize("device", DEVICES)
