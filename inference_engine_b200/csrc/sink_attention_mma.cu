@@ -294,6 +294,7 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
     }
 }
 
+constexpr int MERGE_MAX_SPLITS = 1024;
 // grid: tokens * heads.  Merges a token and head's ranges in rising order: maxima and sums are in units
 // of log2 e; the sink (if any) is one more term of the sum; the gate multiplies the result.
 __global__ void __launch_bounds__(128)
@@ -305,23 +306,32 @@ sink_attention_merge_kernel(const float* __restrict__ partial, const int* __rest
     int token = blockIdx.x / heads, head = blockIdx.x - token * heads;
     if (token >= cu_q[num_seqs]) return;  // (a captured step's padding belongs to no request)
     const float* src = partial + ((size_t)token * heads + head) * splits * (DV + 2);
+    // the ranges' maxima and sums first, all at once (a range per thread), then the rows
+    __shared__ float s_m[MERGE_MAX_SPLITS], s_l[MERGE_MAX_SPLITS];
+    for (int s = threadIdx.x; s < splits; s += 128) {
+        s_m[s] = src[(size_t)s * (DV + 2) + DV];
+        s_l[s] = src[(size_t)s * (DV + 2) + DV + 1];
+    }
+    __syncthreads();
     float m = sinks != nullptr ? sinks[head] * LOG2E : -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, src[(size_t)s * (DV + 2) + DV]);
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, s_m[s]);
     float l = sinks != nullptr ? exp2f(sinks[head] * LOG2E - m) : 0.f;
     if (m == -INFINITY) m = 0.f;
     float acc[(DV + 127) / 128];
 #pragma unroll
     for (int i = 0; i < (DV + 127) / 128; ++i) acc[i] = 0.f;
+#pragma unroll 4
     for (int s = 0; s < splits; ++s) {
         const float* row = src + (size_t)s * (DV + 2);
-        float ms = row[DV];
-        if (ms == -INFINITY) continue;  // (an empty range: its sums were never written)
-        float w = exp2f(ms - m);
-        l += row[DV + 1] * w;
+        float ms = s_m[s];
+        bool empty = ms == -INFINITY;  // (an empty range: its sums were never written)
+        float w = empty ? 0.f : exp2f(ms - m);
+        l = fmaf(s_l[s], w, l);
 #pragma unroll
         for (int i = 0; i < (DV + 127) / 128; ++i) {
             int c = i * 128 + threadIdx.x;
-            if (c < DV) acc[i] = fmaf(row[c], w, acc[i]);
+            float v = (c < DV && !empty) ? row[c] : 0.f;
+            acc[i] = fmaf(v, w, acc[i]);
         }
     }
     float f = l > 0.f ? 1.0f / l : 0.f;
@@ -356,7 +366,8 @@ IE_API int ie_sink_attention_mma(const void* q, const void* k_cache, const void*
     if (partial != nullptr) {
         // ranges of key tiles: a request's tokens times the heads of a group are one tile of rows, and
         // the scratch holds [num_tokens, heads, splits, DV + 2] floats
-        if (max_q_len * (heads / kv_heads) > ROWS || splits < 1 || tiles_per_split < 1 || num_tokens < 1)
+        if (max_q_len * (heads / kv_heads) > ROWS || splits < 1 || splits > MERGE_MAX_SPLITS || tiles_per_split < 1 ||
+            num_tokens < 1)
             return (int)cudaErrorInvalidValue;
         int rc = ie_launch(sink_attention_mma_kernel, dim3(splits, kv_heads, num_seqs), dim3(THREADS), smem,
                            (cudaStream_t)stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,

@@ -127,6 +127,8 @@ class CudaOps:
         self._sigattn_libs: dict[tuple[int, int], object] = {}
         self._sinkattn_libs: dict[tuple[int, int], object] = {}
         self.sink_mma = os.environ.get("IE_B200_SINK_MMA", "1") != "0"  # tensor-core sink attention
+        # residual gates' products as partial sums: faster by themselves, slower inside a captured step
+        self.gate_split = os.environ.get("IE_B200_GATE_SPLIT", "0") == "1"
         self.sigmoid_mma = os.environ.get("IE_B200_SIGMOID_MMA", "1") != "0"  # tensor-core sigmoid attention
         self._argmax_scratch = None
         self._tickets = None

@@ -151,9 +151,10 @@ class GatedPreNormResidualBlock(Block):
     def _gate(self, which: str, x, ctx) -> ResidualGate:
         import torch
 
-        # (the product may come back as partial sums: the kernel that applies the gate adds them)
+        # (the product may come back as partial sums if the kernel set says so: the kernel that applies
+        # the gate adds them)
         pre = ctx.ops.linear(x, self.w_gate[which], ws=ctx.ws, tag="resgate." + which, out_dtype=torch.float32,
-                             allow_split=True)
+                             allow_split=getattr(ctx.ops, "gate_split", False))
         return ResidualGate(pre, self.gate_bias[which])
 
     @property
