@@ -34,22 +34,44 @@ route_topk_kernel(const T* __restrict__ x, const float* __restrict__ w, const fl
     int n = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     for (int i = tid; i < width; i += ROUTE_THREADS) xs[i] = ie_load(x + (size_t)n * width + i);
     __syncthreads();
-    for (int e = warp; e < experts; e += ROUTE_THREADS / 32) {
-        const float* we = w + (size_t)e * width;
-        float acc = 0.f;
-        if (width % 4 == 0) {  // (four partial sums per lane, added in a fixed order)
-            float a4[4] = {0.f, 0.f, 0.f, 0.f};
+    // A warp takes the experts warp, warp + 8, ...; four of them at a time, so that four rows' loads are
+    // on their way together.  An expert's sum is the same chain of operations whichever way it is grouped.
+    constexpr int WARPS = ROUTE_THREADS / 32, AT_ONCE = 4;
+    for (int e0 = warp; e0 < experts; e0 += WARPS * AT_ONCE) {
+        float acc[AT_ONCE];
+        if (width % 4 == 0) {  // (four partial sums per lane and expert, added in a fixed order)
+            float a4[AT_ONCE][4];
+#pragma unroll
+            for (int u = 0; u < AT_ONCE; ++u) a4[u][0] = a4[u][1] = a4[u][2] = a4[u][3] = 0.f;
             for (int i = lane * 4; i < width; i += 128) {
-                float4 wv = *reinterpret_cast<const float4*>(we + i);
-                a4[0] = fmaf(xs[i], wv.x, a4[0]); a4[1] = fmaf(xs[i + 1], wv.y, a4[1]);
-                a4[2] = fmaf(xs[i + 2], wv.z, a4[2]); a4[3] = fmaf(xs[i + 3], wv.w, a4[3]);
+                float4 xv = *reinterpret_cast<const float4*>(xs + i);
+#pragma unroll
+                for (int u = 0; u < AT_ONCE; ++u) {
+                    int e = e0 + u * WARPS;
+                    if (e < experts) {
+                        float4 wv = *reinterpret_cast<const float4*>(w + (size_t)e * width + i);
+                        a4[u][0] = fmaf(xv.x, wv.x, a4[u][0]); a4[u][1] = fmaf(xv.y, wv.y, a4[u][1]);
+                        a4[u][2] = fmaf(xv.z, wv.z, a4[u][2]); a4[u][3] = fmaf(xv.w, wv.w, a4[u][3]);
+                    }
+                }
             }
-            acc = (a4[0] + a4[1]) + (a4[2] + a4[3]);
+#pragma unroll
+            for (int u = 0; u < AT_ONCE; ++u) acc[u] = (a4[u][0] + a4[u][1]) + (a4[u][2] + a4[u][3]);
         } else {
-            for (int i = lane; i < width; i += 32) acc = fmaf(xs[i], we[i], acc);
+#pragma unroll
+            for (int u = 0; u < AT_ONCE; ++u) {
+                int e = e0 + u * WARPS;
+                acc[u] = 0.f;
+                if (e < experts)
+                    for (int i = lane; i < width; i += 32) acc[u] = fmaf(xs[i], w[(size_t)e * width + i], acc[u]);
+            }
         }
-        acc = warp_sum(acc);
-        if (lane == 0) score[e] = bias != nullptr ? acc + bias[e] : acc;
+#pragma unroll
+        for (int u = 0; u < AT_ONCE; ++u) {
+            int e = e0 + u * WARPS;
+            float total = warp_sum(acc[u]);
+            if (lane == 0 && e < experts) score[e] = bias != nullptr ? total + bias[e] : total;
+        }
     }
     __syncthreads();
     if (warp != 0) return;

@@ -1359,6 +1359,9 @@ class CudaOps:
                 longest, nh, nkv, page_size, k_cache.shape[0], scale, int(window or 0), self._ptr(sinks),
                 self._ptr(gate), 0 if gate is None else gate.stride(0), self._ptr(scratch), splits, per_split,
                 ctx.num_tokens, self._err_ptr, self._stream()), "sink_attention_mma")
+            if scratch is not None:  # (the call launched the merge kernel too)
+                self.launches += 1
+                self.launch_counts["sink_attention_merge"] = self.launch_counts.get("sink_attention_merge", 0) + 1
             return
         self._check(self._paged_attention_generic(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q),
