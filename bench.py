@@ -570,8 +570,8 @@ def ravapel_rows(size: str, kinds: dict, peaks: dict, tokens: int, batch: int, c
 VOFANEX_SIZES = {
     # width, (gla: heads, dim, vdim, rank, tau), (attention: heads, kv_heads, dim, vdim, window),
     # dense ff, (experts: ff, count, top)
-    "w1024": (1024, (8, 128, 128, 16, 16.0), (16, 4, 64, 64, 512), 4096, (512, 16, 4)),
-    "w2048": (2048, (16, 128, 128, 32, 16.0), (16, 4, 128, 128, 1024), 8192, (1024, 32, 4)),
+    "w1024": (1024, (8, 128, 128, 16, 8.0), (16, 4, 64, 64, 512), 4096, (512, 16, 4)),
+    "w2048": (2048, (16, 128, 128, 32, 8.0), (16, 4, 128, 128, 1024), 8192, (1024, 32, 4)),
 }
 
 

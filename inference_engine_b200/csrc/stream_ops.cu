@@ -174,13 +174,14 @@ sandwich_norm_kernel(float* __restrict__ h, const float* __restrict__ delta, int
 
 __device__ __forceinline__ float sigmoid_precise(float z) { return 1.0f / (1.0f + expf(-z)); }
 
-// gate_pre: [N, hidden] 32-bit (rows as in h), or `gate_partials` such arrays `gate_stride` apart, the parts
-// of a split product, added in order; gate_bias: [hidden] or null.  `rows` selects rows and
+// gate_pre: [N, hidden] 32-bit (rows as in h, `gate_ld` numbers apart: it may be some columns of a wider
+// product), or `gate_partials` such arrays `gate_stride` apart, the parts of a split product, added in
+// order; gate_bias: [hidden] or null.  `rows` selects rows and
 // leaves h as it is; out == null: only h is brought up to date.
 template <typename OutT, int VEC>
 __global__ void __launch_bounds__(SN_THREADS)
 gated_add_norm_kernel(float* __restrict__ h, const float* __restrict__ delta, int num_partials, size_t partial_stride,
-                      const float* __restrict__ gate_pre, int gate_partials, size_t gate_stride,
+                      const float* __restrict__ gate_pre, int gate_partials, size_t gate_stride, int gate_ld,
                       const float* __restrict__ gate_bias, const float* __restrict__ weight, float eps,
                       OutT* __restrict__ out, const int* __restrict__ rows, int hidden) {
     extern __shared__ __align__(16) float row_buf[];  // [hidden]
@@ -189,6 +190,7 @@ gated_add_norm_kernel(float* __restrict__ h, const float* __restrict__ delta, in
     ie_pdl_wait();
     int r = blockIdx.x;
     size_t src = (size_t)(rows ? rows[r] : r) * hidden;
+    size_t gsrc = (size_t)(rows ? rows[r] : r) * gate_ld;
     float ss = 0.f;
     for (int i = threadIdx.x * VEC; i < hidden; i += SN_THREADS * VEC) {
         Pack<VEC> y = load_pack<VEC>(delta + src + i);
@@ -197,9 +199,9 @@ gated_add_norm_kernel(float* __restrict__ h, const float* __restrict__ delta, in
 #pragma unroll
             for (int v = 0; v < VEC; ++v) y.v[v] += d.v[v];
         }
-        Pack<VEC> g = load_pack<VEC>(gate_pre + src + i), x = load_pack<VEC>(h + src + i);
+        Pack<VEC> g = load_pack<VEC>(gate_pre + gsrc + i), x = load_pack<VEC>(h + src + i);
         for (int p = 1; p < gate_partials; ++p) {
-            Pack<VEC> d = load_pack<VEC>(gate_pre + p * gate_stride + src + i);
+            Pack<VEC> d = load_pack<VEC>(gate_pre + p * gate_stride + gsrc + i);
 #pragma unroll
             for (int v = 0; v < VEC; ++v) g.v[v] += d.v[v];
         }
@@ -429,17 +431,17 @@ IE_API int ie_weighted_sum(const float* a, float sa, const float* b, float sb, f
 // `delta` is the sum of `num_partials` arrays; `out` may be null (only h is brought up to date);
 // `rows` selects rows, and then h is not modified.
 IE_API int ie_gated_add_norm(float* h, const float* delta, int num_partials, long long partial_stride,
-                             const float* gate_pre, int gate_partials, long long gate_stride,
+                             const float* gate_pre, int gate_partials, long long gate_stride, int gate_ld,
                              const float* gate_bias, const float* weight, float eps,
                              void* out, int out_dtype, const int* rows, int num_rows, int hidden, void* stream) {
     if (num_rows <= 0) return 0;
-    if (delta == nullptr || gate_pre == nullptr || num_partials < 1 || gate_partials < 1)
+    if (delta == nullptr || gate_pre == nullptr || num_partials < 1 || gate_partials < 1 || gate_ld < hidden)
         return (int)cudaErrorInvalidValue;
     if (out != nullptr && weight == nullptr) return (int)cudaErrorInvalidValue;
     size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
-    bool vec = hidden % 4 == 0 && (size_t)partial_stride % 4 == 0 && (size_t)gate_stride % 4 == 0 &&
+    bool vec = hidden % 4 == 0 && (size_t)partial_stride % 4 == 0 && (size_t)gate_stride % 4 == 0 && gate_ld % 4 == 0 &&
                ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(delta) |
                  reinterpret_cast<uintptr_t>(gate_pre) | reinterpret_cast<uintptr_t>(gate_bias) |
                  reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(out)) % 16 == 0);
@@ -452,7 +454,7 @@ IE_API int ie_gated_add_norm(float* h, const float* delta, int num_partials, lon
         }                                                                                                          \
         return ie_launch(gated_add_norm_kernel<T, V>, dim3(num_rows), dim3(SN_THREADS), smem, s, h, delta,         \
                          num_partials, (size_t)partial_stride, gate_pre, gate_partials, (size_t)gate_stride,       \
-                         gate_bias, weight, eps, (T*)out, rows, hidden);                                           \
+                         gate_ld, gate_bias, weight, eps, (T*)out, rows, hidden);                                  \
     } while (0)
     if (out_dtype == IE_BF16) {
         if (vec) IE_GN_LAUNCH(__nv_bfloat16, 4);

@@ -224,7 +224,7 @@ class CudaOps:
             "ie_silu_mul_bias": [P, I, P, P, I, I, I, P],
             "ie_concat_cast": [P, P, P, I, I, I, P],
             "ie_weighted_sum": [P, F, P, F, P, L, P],
-            "ie_gated_add_norm": [P, P, I, L, P, I, L, P, P, F, P, I, P, I, I, P],
+            "ie_gated_add_norm": [P, P, I, L, P, I, L, I, P, P, F, P, I, P, I, I, P],
             "ie_polynorm": [P, I, P, F, P, I, I, I, P],
         }
         for name, args in sigs.items():
@@ -1139,16 +1139,16 @@ class CudaOps:
         """``h += sigmoid(gate_pre + gate_bias) * delta`` element by element (not with ``rows``, which
         selects rows and leaves ``h``); ``out = rms(h) * weight`` unless ``out`` is None.  ``delta`` may be
         the parts of a split product (``[S, N, hidden]``), and so may ``gate_pre`` (32-bit, ``[N, hidden]``
-        or ``[S', N, hidden]``)."""
+        or ``[S', N, hidden]``); a two-dimensional ``gate_pre`` may be some columns of a wider array."""
         if (gate_pre.dtype != self.torch.float32 or tuple(gate_pre.shape[-2:]) != tuple(h.shape)
-                or not gate_pre.is_contiguous()):
+                or gate_pre.stride(-1) != 1 or (gate_pre.dim() == 3 and not gate_pre.is_contiguous())):
             raise KernelError("gated_add_norm: the gate's pre-activation must be a 32-bit array like the stream")
         n = h.shape[0] if rows is None else rows.shape[0]
         parts, stride = self._partials(delta)
         gate_parts, gate_stride = self._partials(gate_pre)
         self._check(self._gated_add_norm(
             h.data_ptr(), delta.data_ptr(), parts, stride, gate_pre.data_ptr(), gate_parts, gate_stride,
-            self._ptr(gate_bias),
+            gate_pre.stride(-2), self._ptr(gate_bias),
             self._ptr(weight), eps, self._ptr(out), _dtype_code(out) if out is not None else 0, self._ptr(rows), n,
             h.shape[1], self._stream()), "gated_add_norm")
 

@@ -148,6 +148,39 @@ class Mixer(Part):
     def forward(self, x, ctx, binding: CacheBinding | None):
         raise NotImplementedError
 
+    # A mixer whose first step is one matrix product over its input can carry the rows of another
+    # linear map of the same input in that product (a block's residual gate, for one): it says so
+    # with ``accepts_input_rows``, is handed the rows before its own ``bind`` (``take_input_rows``)
+    # and leaves their 32-bit products of the step, ``[N, rows]`` as columns of its product, in
+    # ``extra_out`` when it runs.
+    accepts_input_rows = False
+    extra_out = None
+    _extra_rows = None
+
+    def take_input_rows(self, rows) -> None:
+        if not self.accepts_input_rows:
+            raise ValueError(f"{type(self).__name__} has no input product that could carry more rows")
+        self._extra_rows = rows
+
+    def _with_extra_rows(self, own_rows: list):
+        """``(weight, first column of the extra rows' products)``: the mixer's own row blocks, zero
+        rows up to a multiple of four (so that the extra columns can be read four at a time), then
+        the rows it was handed."""
+        import torch
+
+        count = sum(r.shape[0] for r in own_rows)
+        if self._extra_rows is None:
+            return torch.cat(own_rows).contiguous(), count
+        pad = -count % 4
+        if pad:
+            own_rows = own_rows + [own_rows[0].new_zeros(pad, own_rows[0].shape[1])]
+        extra = self._extra_rows.to(own_rows[0].dtype)
+        self._extra_count = extra.shape[0]
+        return torch.cat(own_rows + [extra]).contiguous(), count + pad
+
+    def _extra_columns(self, proj, at: int):
+        return None if self._extra_rows is None else proj[:, at: at + self._extra_count]
+
 
 class FeedForward(Part):
     category = "feed_forward"

@@ -16,10 +16,13 @@ sublayer has one, and the norm).
 the stream: ``x <- x + sigmoid(W1 h + b1) * mixer(h)`` with ``h = norm(x)``, then the same with
 ``W2``, ``b2`` and the feed-forward.  The gate reads what the sublayer reads.  Its product runs in
 the compute dtype with 32-bit sums; sigmoid, multiplication and add are 32-bit and sit in the
-kernel of the next norm (the pending delta travels with its gate: ``output_post``).
+kernel of the next norm (the pending delta travels with its gate: ``output_post``).  A mixer that
+starts with one product over its input carries the mixer gate's rows in that product.
 """
 
 from __future__ import annotations
+
+import os
 
 from .base import Block, BuildEnv, CacheBinding, WeightDecl
 from .norm import PostNorm, ResidualGate
@@ -147,6 +150,11 @@ class GatedPreNormResidualBlock(Block):
                 self.w_gate[which] = tensors[self.names[which]].to(self.dtype).contiguous()
                 bias = self.names.get(which + "_bias")
                 self.gate_bias[which] = tensors[bias].float().contiguous() if bias else None
+        # The mixer's gate reads what the mixer reads: a mixer that starts with one product over its
+        # input takes the gate's rows into that product (this runs before the mixer's own bind).
+        if self.mixer.accepts_input_rows and os.environ.get("IE_B200_GATE_IN_MIXER", "1") != "0":
+            self.mixer.take_input_rows(self.w_gate["mixer_gate"])
+            self.w_gate["mixer_gate"] = None
 
     def _gate(self, which: str, x, ctx) -> ResidualGate:
         import torch
@@ -168,8 +176,11 @@ class GatedPreNormResidualBlock(Block):
         else:
             x = self.pre_mixer.add_norm(h, delta, ctx, tag="norm.mixer", delta_scale=delta_scale,
                                         delta_post=delta_post)
-        gate = self._gate("mixer_gate", x, ctx)
+        in_mixer = self.w_gate["mixer_gate"] is None
+        gate = None if in_mixer else self._gate("mixer_gate", x, ctx)
         mixed = self.mixer.forward(x, ctx, binding)
+        if in_mixer:
+            gate = ResidualGate(self.mixer.extra_out, self.gate_bias["mixer_gate"])
         if self.feed_forward is None:
             self._pending = gate
             return mixed

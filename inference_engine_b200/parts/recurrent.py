@@ -201,6 +201,7 @@ class MLSTM(Mixer):
 @register_part("mixer", "gla")
 class GatedLinearAttention(Mixer):
     allow_split = True
+    accepts_input_rows = True
 
     def __init__(self, *, names: dict, hidden_size: int, heads: int, dim: int, vdim: int, rank: int, tau: float,
                  eps: float, dtype) -> None:
@@ -233,7 +234,8 @@ class GatedLinearAttention(Mixer):
         import torch
 
         n = self.names
-        self.w_in = torch.cat([tensors[n[k]].to(self.dtype) for k in ("q", "k", "v", "g", "a1")]).contiguous()
+        self.w_in, self.extra_at = self._with_extra_rows(
+            [tensors[n[k]].to(self.dtype) for k in ("q", "k", "v", "g", "a1")])
         self.w_o = tensors[n["o"]].to(self.dtype).contiguous()
         self.w_a2 = tensors[n["a2"]].float().contiguous()  # the decay's second map stays 32-bit
         self.a2_bias = tensors[n["a2_bias"]].float().contiguous()
@@ -249,6 +251,7 @@ class GatedLinearAttention(Mixer):
         group = ctx.groups[binding.group]
         ops, ws = ctx.ops, ctx.ws
         proj = ops.linear(x, self.w_in, ws=ws, tag="gla.in", out_dtype=f32)
+        self.extra_out = self._extra_columns(proj, self.extra_at)
         at_g, at_a = 2 * qk + vs, 2 * qk + 2 * vs
         decay = ws.buffer("gla.decay", n, qk, f32)
         ops.lowrank_decay(proj[:, at_a: at_a + self.rank], self.w_a2, self.a2_bias, self.tau, decay)

@@ -25,6 +25,7 @@ from .registry import register_part
 @register_part("mixer", "sink_attention")
 class SinkAttention(Mixer):
     allow_split = True
+    accepts_input_rows = True
 
     def __init__(self, *, names: dict, hidden_size: int, heads: int, kv_heads: int, dim: int, vdim: int,
                  scale: float, window: int | None, value_norm: bool, eps: float, position, dtype) -> None:
@@ -76,7 +77,7 @@ class SinkAttention(Mixer):
         rows = [tensors[n[k]].to(self.dtype) for k in "qkv"]
         if "head_gate" in n:
             rows.append(tensors[n["head_gate"]].to(self.dtype))
-        self.w_in = torch.cat(rows).contiguous()
+        self.w_in, self.extra_at = self._with_extra_rows(rows)
         self.w_o = tensors[n["o"]].to(self.dtype).contiguous()
         if "q_bias" in n:
             self.bias = torch.cat([tensors[n[k]].float() for k in ("q_bias", "k_bias", "v_bias")]).contiguous()
@@ -94,13 +95,14 @@ class SinkAttention(Mixer):
         k_cache, v_cache = group.k[binding.slot], group.v[binding.slot]
         ops, ws = ctx.ops, ctx.ws
         proj = ops.linear(x, self.w_in, ws=ws, tag="sinkattn.in", out_dtype=torch.float32)
+        self.extra_out = self._extra_columns(proj, self.extra_at)
         q = ws.buffer("sinkattn.q", n, self.heads * self.dim, self.dtype)
         table = self.position.rotary_table() if self.position is not None else None
         rot_dims = self.position.rotary_dim if self.position is not None else 0
         ops.qk_norm_rope_write(proj, ctx.positions, table, rot_dims, None, None, self.eps, q, k_cache, v_cache,
                                group.slot_mapping if binding.writes else None, self.heads, self.kv_heads,
                                self.dim, self.vdim, group.page_size, bias=self.bias, value_norm=self.value_norm)
-        gate = proj[:, self.qkv_size:] if "head_gate" in self.names else None
+        gate = proj[:, self.qkv_size: self.qkv_size + self.heads] if "head_gate" in self.names else None
         out = ws.buffer("sinkattn.out", n, self.heads * self.vdim, self.dtype)
         ops.sink_attention(q, k_cache, v_cache, group.block_tables, ctx, self.heads, self.kv_heads, self.dim,
                            self.vdim, group.page_size, self.scale, self.window, self.sinks, gate, out)

@@ -393,7 +393,7 @@ def test_sink_attention_on_the_tensor_cores(d, dv, window):
 
 
 @pytest.mark.parametrize("device", DEVICES)
-@pytest.mark.parametrize("heads,dim,vdim,rank,tau", [(3, 12, 20, 5, 8.0), (1, 5, 3, 1, 1.0), (2, 48, 16, 16, 16.0),
+@pytest.mark.parametrize("heads,dim,vdim,rank,tau", [(3, 12, 20, 5, 8.0), (1, 5, 3, 1, 1.0), (2, 48, 16, 16, 32.0),
                                                      (2, 100, 40, 7, 2.5), (1, 130, 8, 300, 4.0), (1, 260, 33, 3, 64.0)])
 def test_gated_linear_attention_in_pieces(device, heads, dim, vdim, rank, tau):
     """The decay from its low-rank map and the recurrence over 61 tokens cut into pieces of 1 to 17
@@ -499,6 +499,13 @@ def test_gated_add_and_norm_in_one_kernel(device, hidden):
             hd3 = h.clone().to(device)
             ops.gated_add_norm(hd3, parts.to(device), pre.to(device), dev_b, None, 0.0, None)
             torch.testing.assert_close(hd3.cpu(), h_want.float(), atol=1e-5, rtol=1e-5)
+            # the gate may be some columns of a wider product (on a 16-byte boundary or not)
+            for lead in (4, 3):
+                wide = torch.cat([torch.full((n, lead), 9.0), pre, torch.full((n, 2), 9.0)], dim=1).to(device)
+                hd5, out5 = h.clone().to(device), torch.zeros(n, hidden, device=device)
+                ops.gated_add_norm(hd5, parts.to(device), wide[:, lead: lead + hidden], dev_b, w.to(device), eps, out5)
+                torch.testing.assert_close(hd5.cpu(), h_want.float(), atol=1e-5, rtol=1e-5)
+                torch.testing.assert_close(out5.cpu(), out_want.float(), atol=1e-5, rtol=1e-5)
             # the gate's product may arrive in parts too
             halves = torch.stack([pre * 0.25, pre * 0.75]).to(device)
             hd4, out4 = h.clone().to(device), torch.zeros(n, hidden, device=device)
@@ -508,7 +515,7 @@ def test_gated_add_and_norm_in_one_kernel(device, hidden):
 
 
 @pytest.mark.parametrize("device", DEVICES)
-@pytest.mark.parametrize("experts,top", [(8, 3), (5, 1), (3, 3), (2, 1), (7, 6), (64, 8)])
+@pytest.mark.parametrize("experts,top", [(9, 3), (5, 1), (3, 3), (2, 1), (7, 6), (64, 8)])
 def test_router_with_a_bias_weighs_only_the_chosen(device, experts, top):
     """The bias decides who is chosen (it is as large as the logits), and the weights are the
     softmax over the chosen logits alone."""

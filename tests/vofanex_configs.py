@@ -50,7 +50,7 @@ MIXED = config(72, 131, [
 # attention first; a window wider than any prompt and one of a single position; every expert used
 ATTENTION_FIRST = config(64, 97, [
     (attention(4, 2, 16, 8, window=500), dense(96)),
-    (gla(2, 16, 16, tau=16.0), moe(3, 3, 20)),
+    (gla(2, 16, 16, tau=12.0), moe(3, 3, 20)),
     (attention(2, 1, 24, 40, window=1), None),
     (gla(4, 8, 8, tau=2.0), dense(32)),
 ], scale=1.0)
@@ -63,7 +63,7 @@ ODD = config(50, 61, [
 ], scale=0.5)
 # sizes the bfloat16 tensor-core kernels take, windows that span several tiles and pages of 16
 WIDE = config(128, 211, [
-    (gla(4, 32, 64, tau=16.0), dense(192)),
+    (gla(4, 32, 64, tau=20.0), dense(192)),
     (attention(8, 2, 64, 32, window=100), moe(8, 2, 64)),
     (gla(2, 64, 32, tau=6.0), dense(160)),
     (attention(4, 4, 32, 64, window=40), dense(128)),
