@@ -597,11 +597,15 @@ def vofanex_rows(size: str, kinds: dict, peaks: dict, tokens: int, batch: int, c
     H, G, d, dv, window = at
     eff, experts, top = ex
     used = min(experts, batch * top if decode else experts)
+    def with_gate(rows: int) -> int:  # a sublayer's input product carries its residual gate's rows behind a pad
+        return rows + (-rows % 4) + width
+
     weights = {  # elements of the matrix a launch reads
-        "linear:gla.in": width * (gl[0] * (2 * gl[1] + 2 * gl[2]) + gl[3]), "linear:gla.delta": width * gl[0] * gl[2],
-        "linear:sinkattn.in": width * ((H + G) * d + G * dv + H), "linear:sinkattn.delta": width * H * dv,
+        "linear:gla.in": width * with_gate(gl[0] * (2 * gl[1] + 2 * gl[2]) + gl[3]),
+        "linear:gla.delta": width * gl[0] * gl[2],
+        "linear:sinkattn.in": width * with_gate((H + G) * d + G * dv + H), "linear:sinkattn.delta": width * H * dv,
         "linear:resgate.mixer_gate": width * width, "linear:resgate.feed_forward_gate": width * width,
-        "linear:ffn.up32": width * ff, "linear:ffn.delta": width * ff, "linear:head": width * DESIGN_VOCAB,
+        "linear:ffn.up32": width * with_gate(ff), "linear:ffn.delta": width * ff, "linear:head": width * DESIGN_VOCAB,
         "routed.gate_up": 2 * eff * width * used, "routed.down": eff * width * used,
     }
     flops = {  # per prompt launch

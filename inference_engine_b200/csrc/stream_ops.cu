@@ -228,19 +228,19 @@ gated_add_norm_kernel(float* __restrict__ h, const float* __restrict__ delta, in
     }
 }
 
-// One block per row of `z` ([N, width], 32-bit or the compute dtype); coeff: a, b, c, e.
+// One block per row of `z` ([N, width], rows `z_ld` numbers apart, 32-bit or the compute dtype); coeff: a, b, c, e.
 template <typename InT, typename OutT>
 __global__ void __launch_bounds__(SN_THREADS)
-polynorm_kernel(const InT* __restrict__ z, const float* __restrict__ coeff, float eps, OutT* __restrict__ out,
-                int width) {
+polynorm_kernel(const InT* __restrict__ z, int z_ld, const float* __restrict__ coeff, float eps,
+                OutT* __restrict__ out, int width) {
     extern __shared__ __align__(16) float row_buf[];  // [width]
     __shared__ float red[SN_THREADS / 32];
     ie_pdl_trigger();
     ie_pdl_wait();
-    size_t at = (size_t)blockIdx.x * width;
+    size_t at = (size_t)blockIdx.x * width, z_at = (size_t)blockIdx.x * z_ld;
     float s2 = 0.f, s4 = 0.f, s6 = 0.f;
     for (int i = threadIdx.x; i < width; i += SN_THREADS) {
-        float x = ie_load(z + at + i), x2 = x * x, x3 = x2 * x;
+        float x = ie_load(z + z_at + i), x2 = x * x, x3 = x2 * x;
         row_buf[i] = x;
         s2 += x2;
         s4 = fmaf(x2, x2, s4);
@@ -466,9 +466,10 @@ IE_API int ie_gated_add_norm(float* h, const float* delta, int num_partials, lon
 }
 
 // `z` is 32-bit or has the output's dtype.
-IE_API int ie_polynorm(const void* z, int in_dtype, const float* coeff, float eps, void* out, int out_dtype,
-                       int num_rows, int width, void* stream) {
+IE_API int ie_polynorm(const void* z, int z_ld, int in_dtype, const float* coeff, float eps, void* out,
+                       int out_dtype, int num_rows, int width, void* stream) {
     if (num_rows <= 0 || width <= 0) return 0;
+    if (z_ld < width) return (int)cudaErrorInvalidValue;
     size_t smem = (size_t)width * sizeof(float);
     if (smem > 200 * 1024 || (in_dtype != IE_F32 && in_dtype != out_dtype)) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
@@ -479,8 +480,8 @@ IE_API int ie_polynorm(const void* z, int in_dtype, const float* coeff, float ep
             cudaError_t e = ie_allow_smem(allowed, polynorm_kernel<IN, OUT>, 200 * 1024);                          \
             if (e != cudaSuccess) return (int)e;                                                                   \
         }                                                                                                          \
-        return ie_launch(polynorm_kernel<IN, OUT>, dim3(num_rows), dim3(SN_THREADS), smem, s, (const IN*)z, coeff,  \
-                         eps, (OUT*)out, width);                                                                   \
+        return ie_launch(polynorm_kernel<IN, OUT>, dim3(num_rows), dim3(SN_THREADS), smem, s, (const IN*)z, z_ld,   \
+                         coeff, eps, (OUT*)out, width);                                                            \
     } while (0)
     if (out_dtype == IE_BF16) {
         if (in_dtype == IE_BF16) IE_PN_LAUNCH(__nv_bfloat16, __nv_bfloat16);

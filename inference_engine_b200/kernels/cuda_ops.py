@@ -225,7 +225,7 @@ class CudaOps:
             "ie_concat_cast": [P, P, P, I, I, I, P],
             "ie_weighted_sum": [P, F, P, F, P, L, P],
             "ie_gated_add_norm": [P, P, I, L, P, I, L, I, P, P, F, P, I, P, I, I, P],
-            "ie_polynorm": [P, I, P, F, P, I, I, I, P],
+            "ie_polynorm": [P, I, I, P, F, P, I, I, I, P],
         }
         for name, args in sigs.items():
             fn = getattr(self.lib, name)
@@ -1155,10 +1155,11 @@ class CudaOps:
     @_kind("activation")
     def polynorm(self, z, coeff, eps, out) -> None:
         """``out = a N(z) + b N(z^2) + c N(z^3) + e`` per row with ``coeff = (a, b, c, e)`` and ``N`` the
-        division by the root mean square over the row; ``z`` is 32-bit or has ``out``'s dtype."""
-        if z.dtype not in (self.torch.float32, out.dtype) or z.shape != out.shape or not z.is_contiguous():
-            raise KernelError("polynorm reads contiguous rows, 32-bit or of the output's dtype")
-        self._check(self._polynorm(z.data_ptr(), _dtype_code(z), coeff.data_ptr(), eps, out.data_ptr(),
+        division by the root mean square over the row; ``z`` is 32-bit or has ``out``'s dtype, and may
+        be the first columns of a wider array."""
+        if z.dtype not in (self.torch.float32, out.dtype) or z.shape != out.shape or z.stride(1) != 1:
+            raise KernelError("polynorm reads rows of unit stride, 32-bit or of the output's dtype")
+        self._check(self._polynorm(z.data_ptr(), z.stride(0), _dtype_code(z), coeff.data_ptr(), eps, out.data_ptr(),
                                    _dtype_code(out), z.shape[0], z.shape[1], self._stream()), "polynorm")
 
     # --- recurrent mixers with a decaying matrix state -------------------------------------------

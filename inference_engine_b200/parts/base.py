@@ -136,23 +136,13 @@ class PositionEncoding(Part):
         """Additive encodings add to the embedded tokens here; default: nothing."""
 
 
-class Mixer(Part):
-    category = "mixer"
+class CarriesInputRows:
+    """A sublayer whose first step is one matrix product over its input can carry the rows of another
+    linear map of the same input in that product (a block's residual gate, for one): it says so
+    with ``accepts_input_rows``, is handed the rows before its own ``bind`` (``take_input_rows``)
+    and leaves their 32-bit products of the step, ``[N, rows]`` as columns of its product, in
+    ``extra_out`` when it runs."""
 
-    def cache_request(self) -> PagedKVRequest | StateRequest | None | tuple:
-        """What the mixer keeps per request.  A mixer made of several (two side by side, one
-        wrapped around another) returns a tuple of requests, and is then handed a tuple of
-        bindings in the same order (``None`` where a request is ``None``)."""
-        return None
-
-    def forward(self, x, ctx, binding: CacheBinding | None):
-        raise NotImplementedError
-
-    # A mixer whose first step is one matrix product over its input can carry the rows of another
-    # linear map of the same input in that product (a block's residual gate, for one): it says so
-    # with ``accepts_input_rows``, is handed the rows before its own ``bind`` (``take_input_rows``)
-    # and leaves their 32-bit products of the step, ``[N, rows]`` as columns of its product, in
-    # ``extra_out`` when it runs.
     accepts_input_rows = False
     extra_out = None
     _extra_rows = None
@@ -163,7 +153,7 @@ class Mixer(Part):
         self._extra_rows = rows
 
     def _with_extra_rows(self, own_rows: list):
-        """``(weight, first column of the extra rows' products)``: the mixer's own row blocks, zero
+        """``(weight, first column of the extra rows' products)``: the part's own row blocks, zero
         rows up to a multiple of four (so that the extra columns can be read four at a time), then
         the rows it was handed."""
         import torch
@@ -182,7 +172,20 @@ class Mixer(Part):
         return None if self._extra_rows is None else proj[:, at: at + self._extra_count]
 
 
-class FeedForward(Part):
+class Mixer(CarriesInputRows, Part):
+    category = "mixer"
+
+    def cache_request(self) -> PagedKVRequest | StateRequest | None | tuple:
+        """What the mixer keeps per request.  A mixer made of several (two side by side, one
+        wrapped around another) returns a tuple of requests, and is then handed a tuple of
+        bindings in the same order (``None`` where a request is ``None``)."""
+        return None
+
+    def forward(self, x, ctx, binding: CacheBinding | None):
+        raise NotImplementedError
+
+
+class FeedForward(CarriesInputRows, Part):
     category = "feed_forward"
 
     def forward(self, x, ctx):

@@ -16,8 +16,8 @@ sublayer has one, and the norm).
 the stream: ``x <- x + sigmoid(W1 h + b1) * mixer(h)`` with ``h = norm(x)``, then the same with
 ``W2``, ``b2`` and the feed-forward.  The gate reads what the sublayer reads.  Its product runs in
 the compute dtype with 32-bit sums; sigmoid, multiplication and add are 32-bit and sit in the
-kernel of the next norm (the pending delta travels with its gate: ``output_post``).  A mixer that
-starts with one product over its input carries the mixer gate's rows in that product.
+kernel of the next norm (the pending delta travels with its gate: ``output_post``).  A mixer or
+feed-forward that starts with one product over its input carries its gate's rows in that product.
 """
 
 from __future__ import annotations
@@ -152,9 +152,12 @@ class GatedPreNormResidualBlock(Block):
                 self.gate_bias[which] = tensors[bias].float().contiguous() if bias else None
         # The mixer's gate reads what the mixer reads: a mixer that starts with one product over its
         # input takes the gate's rows into that product (this runs before the mixer's own bind).
-        if self.mixer.accepts_input_rows and os.environ.get("IE_B200_GATE_IN_MIXER", "1") != "0":
-            self.mixer.take_input_rows(self.w_gate["mixer_gate"])
-            self.w_gate["mixer_gate"] = None
+        # The same for a feed-forward and its gate.
+        if os.environ.get("IE_B200_GATE_IN_MIXER", "1") != "0":
+            for which, part in (("mixer_gate", self.mixer), ("feed_forward_gate", self.feed_forward)):
+                if part is not None and part.accepts_input_rows:
+                    part.take_input_rows(self.w_gate[which])
+                    self.w_gate[which] = None
 
     def _gate(self, which: str, x, ctx) -> ResidualGate:
         import torch
@@ -185,5 +188,9 @@ class GatedPreNormResidualBlock(Block):
             self._pending = gate
             return mixed
         x = self.pre_feed_forward.add_norm(h, mixed, ctx, tag="norm.ffn", delta_post=gate)
-        self._pending = self._gate("feed_forward_gate", x, ctx)
-        return self.feed_forward.forward(x, ctx)
+        if self.w_gate["feed_forward_gate"] is not None:
+            self._pending = self._gate("feed_forward_gate", x, ctx)
+            return self.feed_forward.forward(x, ctx)
+        out = self.feed_forward.forward(x, ctx)
+        self._pending = ResidualGate(self.feed_forward.extra_out, self.gate_bias["feed_forward_gate"])
+        return out

@@ -126,7 +126,10 @@ class PolyNormFF(FeedForward):
     """Dense feed-forward without a gate: ``down(act(up(x)))`` with ``act(z) = a N(z) + b N(z^2) +
     c N(z^3) + e``: powers element by element, ``N`` divides a token's vector by its root mean square
     (eps inside the root), and ``(a, b, c, e)`` is a tensor of four numbers.  The first product's
-    sums stay 32-bit for the activation, which rounds once to the compute dtype."""
+    sums stay 32-bit for the activation, which rounds once to the compute dtype.  The first product
+    can carry more rows (``accepts_input_rows``)."""
+
+    accepts_input_rows = True
 
     def __init__(self, *, up_proj: str, down_proj: str, coeff: str, hidden_size: int, intermediate_size: int,
                  eps: float, dtype) -> None:
@@ -146,7 +149,7 @@ class PolyNormFF(FeedForward):
                 self.names["coeff"]: WeightDecl((4,), "vector", "ones_plus_normal")}
 
     def bind(self, tensors, env: BuildEnv) -> None:
-        self.w_up = tensors[self.names["up"]].to(self.dtype).contiguous()
+        self.w_up, self.extra_at = self._with_extra_rows([tensors[self.names["up"]].to(self.dtype)])
         self.w_down = tensors[self.names["down"]].to(self.dtype).contiguous()
         self.coeff = tensors[self.names["coeff"]].float().contiguous()
 
@@ -154,7 +157,8 @@ class PolyNormFF(FeedForward):
         import torch
 
         up = ctx.ops.linear(x, self.w_up, ws=ctx.ws, tag="ffn.up32", out_dtype=torch.float32)
+        self.extra_out = self._extra_columns(up, self.extra_at)
         act = ctx.ws.buffer("ffn.act", x.shape[0], self.intermediate_size, self.dtype)
-        ctx.ops.polynorm(up, self.coeff, self.eps, act)
+        ctx.ops.polynorm(up[:, : self.intermediate_size], self.coeff, self.eps, act)
         return ctx.ops.linear(act, self.w_down, ws=ctx.ws, tag="ffn.delta", out_dtype=torch.float32,
                               allow_split=True)

@@ -468,6 +468,11 @@ def test_polynorm_activation(device, inter):
     out16 = torch.zeros(n, inter, device=device, dtype=torch.bfloat16)
     ops.polynorm(z.to(device), coeff.to(device), eps, out16)
     torch.testing.assert_close(out16.float().cpu(), want, atol=2e-2, rtol=2e-2)
+    # the rows may be the first columns of a wider product
+    wide = torch.cat([z, torch.full((n, 7), 50.0)], dim=1).to(device)
+    out_w = torch.zeros(n, inter, device=device)
+    ops.polynorm(wide[:, :inter], coeff.to(device), eps, out_w)
+    torch.testing.assert_close(out_w.cpu(), want, atol=2e-5, rtol=2e-5)
 
 
 @pytest.mark.parametrize("device", DEVICES)
