@@ -1350,7 +1350,7 @@ class CudaOps:
                 # the tiles between the first row's oldest key and the last row's own position, in
                 # ranges of two: from the window and the row bound alone, so a captured launch stays valid
                 tiles = (int(window) + longest - 2) // 64 + 2
-                per_split = 2
+                per_split = max(2, -(-tiles // 1024))  # (the merge kernel takes up to 1,024 ranges)
                 splits = -(-tiles // per_split)
                 if splits > 1:
                     scratch = self._scratch(ctx, "attn.sink_partial", ctx.num_tokens * nh * splits * (vdim + 2), q.device)
