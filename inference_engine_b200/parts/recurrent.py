@@ -21,7 +21,8 @@ mean square, the heads together are multiplied by a weight and by ``sigmoid(W_g 
 ``v = W_v h``; ``a = sigmoid(W_a2 (W_a1 h) + b)^(1 / tau)`` per head and channel, from a low-rank map of
 the input; ``S <- diag(a) S + k v^T``, ``o = S^T q``; each head's ``o`` is divided by its root mean
 square over ``vdim`` and multiplied by a weight of size ``vdim`` that the heads share; the heads
-together are multiplied by ``silu(W_g h)``; ``W_o``.
+together are multiplied by ``silu(W_g h)``; ``W_o``.  Its input product can carry more rows of another
+map of the same input (``accepts_input_rows``).
 
 Gates, decays, the state and the read-out are 32-bit in every precision; the projections run in
 the compute dtype with 32-bit sums.  The state lives in the request's state slot: ``S`` column by

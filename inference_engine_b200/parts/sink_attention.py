@@ -12,8 +12,9 @@ input) before the output projection.  Query head ``h`` uses key/value head ``h /
 kv_heads)``.  Scores, weights, the value norm and the gate are 32-bit.
 
 Queries, keys, values and the head gates come from one matrix product over the row-concatenated
-weights; biases, value norm and the cache write are one kernel; the gate is applied where the
-attention kernel writes its result.
+weights, which can carry more rows of another map of the same input (``accepts_input_rows``);
+biases, value norm and the cache write are one kernel; the gate is applied where the attention
+kernel writes its result.
 """
 
 from __future__ import annotations
