@@ -1,1 +1,1 @@
-from . import llama, ravapel, rugedra, vofanex  # noqa: F401 (register LlamaForCausalLM, Ravapel, Rugedra and Vofanex)
+from . import llama, puposun, ravapel, rugedra, vofanex  # noqa: F401 (register LlamaForCausalLM, Puposun, Ravapel, Rugedra and Vofanex)

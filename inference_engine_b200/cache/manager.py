@@ -6,7 +6,8 @@ and either all positions or a window of the latest ones).  Each paged group has 
 page pool of its own and one block table per request: entry ``i`` is the page that holds
 positions ``[i * page_size, (i + 1) * page_size)``, or ``-1`` once a window (or, in a group
 whose queries see their own chunk of positions only, the start of the current chunk) has passed
-it and the page was given back.  Token ``p`` lives in flat slot
+it and the page was given back (the pages of the first ``keep_first`` positions of a group that
+keeps them visible stay).  Token ``p`` lives in flat slot
 ``table[p // page_size] * page_size + p % page_size`` (engine/runtime/block_manager.py:171-174).
 
 Pages are taken when a request grows (``grow``), given back when it ends (``free``) or
@@ -32,6 +33,7 @@ class PagedGroupSpec:
     window: int | None = None  # None: every position stays; else the latest ``window`` do
     value_dim: int | None = None  # size of a value row: None = head_dim; 0 = no value rows are kept
     chunk: int | None = None  # queries see their own chunk of this many positions only (None: no chunks)
+    keep_first: int = 0  # with a window: the first positions stay visible, their pages are never given back
 
     @property
     def values_per_token(self) -> int:
@@ -121,6 +123,11 @@ class CacheManager:
     def table(self, group: int, req_id) -> list[int]:
         return self._requests[req_id].tables[group]
 
+    def _kept_pages(self, group: int) -> int:
+        """Pages at the start of a request that a window never passes (they hold kept positions)."""
+        keep = self.paged_groups[group].keep_first
+        return -(-keep // self.page_size) if keep > 0 else 0
+
     def _first_needed_page(self, group: int, first_query_pos: int) -> int:
         spec = self.paged_groups[group]
         first = 0
@@ -139,7 +146,8 @@ class CacheManager:
         for g, table in enumerate(req.tables):
             first = self._first_needed_page(g, num_computed)
             n = 0
-            for i in range(first, last_page):
+            kept = range(min(self._kept_pages(g), first, last_page))
+            for i in [*kept, *range(first, last_page)]:
                 if i >= len(table) or table[i] < 0:
                     n += 1
             needed.append(n)
@@ -182,7 +190,8 @@ class CacheManager:
             first = self._first_needed_page(g, num_computed)
             while len(table) < last_page:
                 table.append(-1)
-            for i in range(first, last_page):
+            kept = range(min(self._kept_pages(g), first, last_page))
+            for i in [*kept, *range(first, last_page)]:
                 if table[i] < 0:
                     table[i] = self.pools[g].allocate()
                     self._mirror(g, req.state_slot, i, table[i])
@@ -221,7 +230,7 @@ class CacheManager:
         freed = 0
         for g, table in enumerate(req.tables):
             first = min(self._first_needed_page(g, num_computed), len(table))
-            for i in range(req.released[g], first):
+            for i in range(max(req.released[g], self._kept_pages(g)), first):
                 if table[i] >= 0:
                     self.pools[g].free(table[i])
                     table[i] = -1

@@ -20,6 +20,9 @@
 // `sinks` != null (softmax only): the denominator holds one more term exp(sinks[head]) that has no
 // key and no value; it is the state the running maximum and sum start from.  `out_gate` != null:
 // the head's result is multiplied by sigmoid(out_gate[token * gate_ld + head]).
+// `softcap` > 0: a score s (after the scale) becomes softcap * tanh(s / softcap).  `keep_first` > 0 (with
+// a window): the keys at positions below `keep_first` stay visible to every later query of the request,
+// beside its window; they keep their own positions.
 #include "common.cuh"
 #include <math.h>
 
@@ -66,7 +69,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                int nh, int nkv, int hd, int hdv, int v_stride, int page_size, int total_pages,
                                float scale, int window, int chunk, const float* __restrict__ head_bias,
                                const float* __restrict__ sinks, const float* __restrict__ out_gate, int gate_ld,
-                               int* err) {
+                               float softcap, int keep_first, int* err) {
     extern __shared__ float q_smem[];  // [WARPS][hd]
     ie_pdl_trigger();
     ie_pdl_wait();
@@ -84,6 +87,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
 
     int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     if (chunk > 0) lo = max(lo, (pos / chunk) * chunk);  // chunks are counted from the request's position 0
+    const int kept = min(keep_first, lo);  // keys below `kept` are seen beside the window's
+    const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
     const bool gated = head_bias != nullptr;  // sigmoid(score + bias) per key, not normalised over keys
     float hb = gated ? head_bias[head] : 0.f;
     float m = -INFINITY, l = 0.f;
@@ -93,9 +98,13 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
     for (int i = 0; i < MAX_ACC; ++i) acc[i] = 0.f;
     int nacc = (hdv + 31) / 32;
 
-    for (int t0 = (lo / 32) * 32; t0 <= pos; t0 += 32) {
+    for (int t0 = kept > 0 ? 0 : (lo / 32) * 32; t0 <= pos; t0 += 32) {
+        if (t0 >= kept && t0 + 31 < lo) {  // between the kept keys and the window: nothing to see
+            t0 = (lo / 32) * 32 - 32;
+            continue;
+        }
         int kpos = t0 + lane;
-        bool valid = kpos >= lo && kpos <= pos;
+        bool valid = (kpos >= lo || kpos < kept) && kpos <= pos;
         long long row = -1;
         float s = -INFINITY;
         if (valid) {
@@ -106,6 +115,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
             } else {
                 row = ((long long)page * nkv + kvh) * page_size + (kpos % page_size);
                 s = (hd % 8 == 0 ? dot_row(qs, k_cache + row * hd, hd) : dot_row_any(qs, k_cache + row * hd, hd)) * scale;
+                if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
             }
         }
         float m_new = m, p;
@@ -150,9 +160,10 @@ IE_API int ie_paged_attention_generic(const void* q, const void* k_cache, const 
                                       int num_tokens, int nh, int nkv, int hd, int hdv, int v_stride,
                                       int page_size, int total_pages, float scale, int window, int chunk,
                                       const float* head_bias, const float* sinks, const float* out_gate,
-                                      int gate_ld, int* err, void* stream) {
+                                      int gate_ld, float softcap, int keep_first, int* err, void* stream) {
     if (num_tokens <= 0) return 0;
     if (hd < 1 || hdv < 1 || hdv > 32 * MAX_ACC || nkv <= 0 || nh % nkv != 0) return (int)cudaErrorInvalidValue;
+    if (keep_first < 0 || softcap < 0.f || (keep_first > 0 && chunk > 0)) return (int)cudaErrorInvalidValue;
     dim3 grid((nh + WARPS - 1) / WARPS, num_tokens);
     size_t smem = (size_t)WARPS * hd * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
@@ -160,11 +171,11 @@ IE_API int ie_paged_attention_generic(const void* q, const void* k_cache, const 
         paged_attention_generic_kernel<<<grid, WARPS * 32, smem, s>>>(
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
             block_tables, table_width, seq_of_token, positions, (__nv_bfloat16*)out,
-            nh, nkv, hd, hdv, v_stride, page_size, total_pages, scale, window, chunk, head_bias, sinks, out_gate, gate_ld, err);
+            nh, nkv, hd, hdv, v_stride, page_size, total_pages, scale, window, chunk, head_bias, sinks, out_gate, gate_ld, softcap, keep_first, err);
     else
         paged_attention_generic_kernel<<<grid, WARPS * 32, smem, s>>>(
             (const float*)q, (const float*)k_cache, (const float*)v_cache,
             block_tables, table_width, seq_of_token, positions, (float*)out,
-            nh, nkv, hd, hdv, v_stride, page_size, total_pages, scale, window, chunk, head_bias, sinks, out_gate, gate_ld, err);
+            nh, nkv, hd, hdv, v_stride, page_size, total_pages, scale, window, chunk, head_bias, sinks, out_gate, gate_ld, softcap, keep_first, err);
     return IE_LAUNCH_CHECK();
 }

@@ -367,6 +367,23 @@ IE_API int ie_scale(float* t, float factor, long long count, void* stream) {
     return ie_launch(scale_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, t, factor, (size_t)count);
 }
 
+// t <- cap * tanh(t * factor / cap): logits (times a constant, if the head has one) squashed into
+// (-cap, cap), 32-bit throughout.
+__global__ void scale_softcap_kernel(float* __restrict__ t, float factor, float cap, size_t count) {
+    ie_pdl_trigger();
+    ie_pdl_wait();
+    float inv = factor / cap;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
+        t[i] = cap * tanhf(t[i] * inv);
+}
+
+IE_API int ie_scale_softcap(float* t, float factor, float cap, long long count, void* stream) {
+    if (count <= 0) return 0;
+    if (!(cap > 0.f)) return (int)cudaErrorInvalidValue;
+    int blocks = (int)((count + 255) / 256 < 8192 ? (count + 255) / 256 : 8192);
+    return ie_launch(scale_softcap_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, t, factor, cap, (size_t)count);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Rotary encoding + cache write            (engine/model/layers.py:82-93, paged_cache.py:42-45)
 //   qkv  : [N, (nh + 2 nkv) * hd] 32-bit, the fused projection's output

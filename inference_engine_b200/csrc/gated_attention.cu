@@ -2,7 +2,10 @@
 // and whose value rows may have another size than its key rows.  Variants by parameters: a bias on
 // the whole projection (`bias`, laid out like a row of it, added first); no norm on queries or keys
 // (their weight is null); value heads divided by their root mean square over `vdim` (eps inside the
-// root, no weight) before they are cached (`value_norm`).
+// root, no weight) before they are cached (`value_norm`); values that are the keys as projected
+// (with their bias, before norm and rotation: `values_from_keys`; the projection then holds no value
+// columns and vdim = dim); the rotation's pairs (`interleaved` 0: entry i with entry i + rot_dims / 2;
+// 1: entry 2i with entry 2i + 1; the table of angles is the same).
 //
 // qk_norm_rope_write: from the fused 32-bit projection [N, ld] = (heads * dim queries, kv_heads *
 // dim keys, kv_heads * vdim values): every query and key head is divided by its root mean square
@@ -22,7 +25,7 @@ template <typename T>
 __global__ void __launch_bounds__(QW_WARPS * 32)
 qk_norm_rope_write_kernel(const float* __restrict__ proj, int ld, const int* __restrict__ positions,
                           const float* __restrict__ table, int rot_dims, int table_positions,
-                          const float* __restrict__ bias, int value_norm,
+                          const float* __restrict__ bias, int value_norm, int values_from_keys, int interleaved,
                           const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
                           T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                           const int* __restrict__ slot_mapping, int heads, int kv_heads, int dim, int vdim,
@@ -50,7 +53,7 @@ qk_norm_rope_write_kernel(const float* __restrict__ proj, int ld, const int* __r
     }
     if (unit >= heads + kv_heads) {  // a value head: copied as it is, or divided by its root mean square
         int g = unit - heads - kv_heads;
-        size_t col = (size_t)(heads + kv_heads) * dim + (size_t)g * vdim;
+        size_t col = values_from_keys ? (size_t)(heads + g) * dim : (size_t)(heads + kv_heads) * dim + (size_t)g * vdim;
         const float* v = src + col;
         const float* vb = bias != nullptr ? bias + col : nullptr;
         float inv = 1.0f;
@@ -92,7 +95,13 @@ qk_norm_rope_write_kernel(const float* __restrict__ proj, int ld, const int* __r
     T* dst = is_q ? q_out + ((size_t)n * heads + unit) * dim : k_cache + cache_row * dim;
     for (int d = lane; d < dim; d += 32) {
         float r = y[d];
-        if (d < half) {
+        if (interleaved) {
+            if (d < rot_dims) {
+                int j = d >> 1;
+                float c = table[((size_t)pos * 2) * half + j], s = table[((size_t)pos * 2 + 1) * half + j];
+                r = (d & 1) ? y[d] * c + y[d - 1] * s : y[d] * c - y[d + 1] * s;
+            }
+        } else if (d < half) {
             float c = table[((size_t)pos * 2) * half + d], s = table[((size_t)pos * 2 + 1) * half + d];
             r = y[d] * c - y[d + half] * s;
         } else if (d < rot_dims) {
@@ -105,7 +114,8 @@ qk_norm_rope_write_kernel(const float* __restrict__ proj, int ld, const int* __r
 }  // namespace
 
 IE_API int ie_qk_norm_rope_write(const float* proj, int ld, const int* positions, const float* table, int rot_dims,
-                                 int table_positions, const float* bias, int value_norm, const float* q_weight,
+                                 int table_positions, const float* bias, int value_norm, int values_from_keys,
+                                 int interleaved, const float* q_weight,
                                  const float* k_weight, float eps,
                                  void* q_out, void* k_cache, void* v_cache, int dtype, const int* slot_mapping,
                                  int num_tokens, int heads, int kv_heads, int dim, int vdim, int page_size,
@@ -113,6 +123,7 @@ IE_API int ie_qk_norm_rope_write(const float* proj, int ld, const int* positions
     if (num_tokens <= 0) return 0;
     if (rot_dims < 0 || rot_dims % 2 || rot_dims > dim || (rot_dims > 0 && table == nullptr))
         return (int)cudaErrorInvalidValue;
+    if (values_from_keys && vdim != dim) return (int)cudaErrorInvalidValue;
     size_t smem = (size_t)QW_WARPS * dim * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
     int units = heads + 2 * kv_heads;
@@ -120,10 +131,10 @@ IE_API int ie_qk_norm_rope_write(const float* proj, int ld, const int* positions
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == IE_BF16)
         return ie_launch(qk_norm_rope_write_kernel<__nv_bfloat16>, grid, dim3(QW_WARPS * 32), smem, s, proj, ld,
-                         positions, table, rot_dims, table_positions, bias, value_norm, q_weight, k_weight, eps, (__nv_bfloat16*)q_out,
+                         positions, table, rot_dims, table_positions, bias, value_norm, values_from_keys, interleaved, q_weight, k_weight, eps, (__nv_bfloat16*)q_out,
                          (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, slot_mapping, heads, kv_heads, dim, vdim,
                          page_size, total_pages, err);
     return ie_launch(qk_norm_rope_write_kernel<float>, grid, dim3(QW_WARPS * 32), smem, s, proj, ld, positions, table,
-                     rot_dims, table_positions, bias, value_norm, q_weight, k_weight, eps, (float*)q_out, (float*)k_cache,
+                     rot_dims, table_positions, bias, value_norm, values_from_keys, interleaved, q_weight, k_weight, eps, (float*)q_out, (float*)k_cache,
                      (float*)v_cache, slot_mapping, heads, kv_heads, dim, vdim, page_size, total_pages, err);
 }

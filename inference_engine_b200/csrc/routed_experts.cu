@@ -3,7 +3,11 @@
 //  * route_topk: per token the router's logits (32-bit; plus a bias per expert if the router has
 //    one), their softmax over all experts, the
 //    groups' best scores, the kept groups, the `top` best allowed experts (ties: the lower index)
-//    and their scores divided by their sum (+ 1e-20).
+//    and their scores divided by their sum (+ 1e-20), times `weight_scale`.  With `sigmoid_scores` an
+//    expert's score is the sigmoid of its logit instead; a `correction` per expert is then added for
+//    the choice alone (groups and experts are chosen by score + correction, the weights are the plain
+//    scores), a group's score is the sum of its `group_top` (1 or 2) largest choice scores, and the
+//    experts of groups that are not kept cannot be chosen whatever their sign.
 //  * routed_align: the step's (token, choice) pairs sorted by expert into tiles of TILE_M rows:
 //    every expert's run of pairs is padded to whole tiles (padding rows are -1), and a list says
 //    which expert each tile belongs to.  One block; nothing goes to the host.
@@ -24,11 +28,14 @@ constexpr int ROUTE_THREADS = 256;
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_THREADS)
 route_topk_kernel(const T* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias, int width,
-                  int experts, int top, int groups, int keep, int* __restrict__ ids, float* __restrict__ weights) {
-    extern __shared__ float sm[];  // x[width], score[experts], group_best[groups]
+                  int experts, int top, int groups, int keep, int sigmoid_scores,
+                  const float* __restrict__ correction, int group_top, float weight_scale,
+                  int* __restrict__ ids, float* __restrict__ weights) {
+    extern __shared__ float sm[];  // x[width], score[experts], group_best[groups], choice[experts]
     float* xs = sm;
     float* score = xs + width;
     float* gbest = score + experts;
+    float* choice = gbest + groups;
     ie_pdl_trigger();
     ie_pdl_wait();
     int n = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -75,6 +82,56 @@ route_topk_kernel(const T* __restrict__ x, const float* __restrict__ w, const fl
     }
     __syncthreads();
     if (warp != 0) return;
+    if (sigmoid_scores) {
+        for (int e = lane; e < experts; e += 32) {
+            float sg = 1.0f / (1.0f + expf(-score[e]));
+            score[e] = sg;
+            choice[e] = correction != nullptr ? sg + correction[e] : sg;
+        }
+        __syncwarp();
+        int per = experts / groups;
+        if (keep < groups) {
+            for (int g = lane; g < groups; g += 32) {  // the group's largest choice scores, one or two of them
+                float b1 = -INFINITY, b2 = -INFINITY;
+                for (int e = g * per; e < (g + 1) * per; ++e) {
+                    float c = choice[e];
+                    if (c > b1) { b2 = b1; b1 = c; }
+                    else if (c > b2) b2 = c;
+                }
+                gbest[g] = (group_top >= 2 && per >= 2) ? b1 + b2 : b1;
+            }
+        }
+        __syncwarp();
+        if (lane != 0) return;
+        if (keep < groups) {
+            for (int round = 0; round < keep; ++round) {  // (a kept group is marked by +inf; ties: the lower index)
+                int best = -1;
+                float bv = -INFINITY;
+                for (int g = 0; g < groups; ++g)
+                    if (gbest[g] != INFINITY && (best < 0 || gbest[g] > bv)) { bv = gbest[g]; best = g; }
+                if (best < 0) break;
+                gbest[best] = INFINITY;
+            }
+            for (int g = 0; g < groups; ++g)
+                if (gbest[g] != INFINITY)
+                    for (int e = g * per; e < (g + 1) * per; ++e) choice[e] = -INFINITY;
+        }
+        float total = 0.f;
+        for (int j = 0; j < top; ++j) {
+            int best = -1;
+            float bv = -INFINITY;
+            for (int e = 0; e < experts; ++e)
+                if (choice[e] > bv) { bv = choice[e]; best = e; }
+            float wj = best < 0 ? 0.f : score[best];
+            ids[(size_t)n * top + j] = best < 0 ? 0 : best;
+            weights[(size_t)n * top + j] = wj;
+            total += wj;
+            if (best >= 0) choice[best] = -INFINITY;  // taken
+        }
+        float f = weight_scale / (total + 1e-20f);
+        for (int j = 0; j < top; ++j) weights[(size_t)n * top + j] *= f;
+        return;
+    }
     // softmax over all experts (lanes share the work, every lane ends with the same numbers)
     float m = -INFINITY;
     for (int e = lane; e < experts; e += 32) m = fmaxf(m, score[e]);
@@ -123,7 +180,7 @@ route_topk_kernel(const T* __restrict__ x, const float* __restrict__ w, const fl
         total += bv < 0.f ? 0.f : bv;
         score[best] = -1.f - score[best];  // taken
     }
-    float f = 1.0f / (total + 1e-20f);
+    float f = weight_scale / (total + 1e-20f);
     for (int j = 0; j < top; ++j) weights[(size_t)n * top + j] *= f;
 }
 
@@ -507,17 +564,22 @@ routed_bf16_kernel(const __nv_bfloat16* __restrict__ a_rows, const __nv_bfloat16
 }  // namespace
 
 IE_API int ie_route_topk(const void* x, int dtype, const float* w, const float* bias, int num_tokens, int width,
-                         int experts, int top, int groups, int keep, int* ids, float* weights, void* stream) {
+                         int experts, int top, int groups, int keep, int sigmoid_scores, const float* correction,
+                         int group_top, float weight_scale, int* ids, float* weights, void* stream) {
     if (num_tokens <= 0) return 0;
     if (experts < 1 || groups < 1 || experts % groups || top < 1 || top > experts) return (int)cudaErrorInvalidValue;
-    size_t smem = (size_t)(width + experts + groups) * sizeof(float);
+    if (group_top < 1 || group_top > 2 || (!sigmoid_scores && (correction != nullptr || group_top != 1)))
+        return (int)cudaErrorInvalidValue;
+    size_t smem = (size_t)(width + 2 * experts + groups) * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == IE_BF16)
         return ie_launch(route_topk_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(ROUTE_THREADS), smem, s,
-                         (const __nv_bfloat16*)x, w, bias, width, experts, top, groups, keep, ids, weights);
+                         (const __nv_bfloat16*)x, w, bias, width, experts, top, groups, keep, sigmoid_scores, correction,
+                         group_top, weight_scale, ids, weights);
     return ie_launch(route_topk_kernel<float>, dim3(num_tokens), dim3(ROUTE_THREADS), smem, s, (const float*)x, w,
-                     bias, width, experts, top, groups, keep, ids, weights);
+                     bias, width, experts, top, groups, keep, sigmoid_scores, correction, group_top, weight_scale, ids,
+                     weights);
 }
 
 IE_API int ie_routed_tile_rows() { return TILE_M; }

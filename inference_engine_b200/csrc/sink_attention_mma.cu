@@ -22,6 +22,12 @@
 // 32-bit scratch row, and a second kernel merges the ranges in rising order, adds the sink's term
 // and applies the gate.  Such a block serves all query heads of one key/value head at once: its rows
 // are (token, head of the group), so a key tile is brought once for the group.
+//
+// `softcap` > 0: a score s (after the scale) becomes softcap * tanh(s / softcap) before the softmax.
+// `keep_first` > 0 (with a window): the keys at positions below `keep_first` stay visible to every later
+// query of the request beside its window, at their own positions.  A block then walks the tiles that
+// hold kept keys and lie wholly before its window's first tile, then the window's tiles; with key
+// ranges cut among blocks the first `kept_splits` ranges are the kept tiles'.
 #include "common.cuh"
 #include <math.h>
 
@@ -64,6 +70,11 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
 }
+// tanh from one exponential: 1 - 2 / (e^(2x) + 1), the argument held where tanh is 1 to 32-bit precision
+__device__ __forceinline__ float tanh_fast(float x) {
+    x = fminf(fmaxf(x, -15.f), 15.f);
+    return 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f);
+}
 __device__ __forceinline__ float quad_max(float x) {
     x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 1));
     return fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 2));
@@ -81,7 +92,8 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
                           __nv_bfloat16* __restrict__ out, int heads, int kv_heads, int page_size,
                           int total_pages, float scale, int window, const float* __restrict__ sinks,
                           const float* __restrict__ out_gate, int gate_ld, float* __restrict__ partial,
-                          int splits, int tiles_per_split, int* err) {
+                          int splits, int tiles_per_split, float softcap, int keep_first, int kept_splits,
+                          int* err) {
     extern __shared__ __align__(16) unsigned char raw[];
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(raw);  // [ROWS][LDK]
     __nv_bfloat16* ks = qs + ROWS * LDK;                        // [2][KEYS][LDK]
@@ -119,7 +131,7 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
         const __nv_bfloat16* ksrc = k_cache;
         const __nv_bfloat16* vsrc = v_cache;
         int bytes = 0;
-        if (pos >= lo_min && pos <= last_pos) {
+        if ((pos >= lo_min || pos < keep_first) && pos <= last_pos) {
             int page = table[pos >> page_shift];
             if (page < 0 || page >= total_pages) {
                 if ((tid & 1) == 0) ie_report(err, page < 0 ? IE_ERR_TABLE : IE_ERR_PAGE, page, q0 + row0);
@@ -137,10 +149,20 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
         for (int c = (tid & 1); c < VC; c += 2) cp_async16z(vd + c * 8, bytes ? vsrc + c * 8 : v_cache, bytes);
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    int t_begin = lo_min / KEYS, t_end = last_pos / KEYS;  // inclusive
+    // The tiles the block walks, by a running number: first the `kept_tiles` tiles that hold kept keys
+    // and lie before the window's first tile (numbers 0 ..), then the window's tiles.
+    const int win_begin = lo_min / KEYS, win_end = last_pos / KEYS;  // inclusive
+    const int kept_tiles = keep_first > 0 ? min((keep_first - 1) / KEYS + 1, win_begin) : 0;
+    auto tile_of = [&](int i) { return i < kept_tiles ? i : win_begin + (i - kept_tiles); };
+    int t_begin = 0, t_end = kept_tiles + (win_end - win_begin);  // running numbers, inclusive
     if (split_mode) {
-        t_begin += blockIdx.x * tiles_per_split;
-        t_end = min(t_end, t_begin + tiles_per_split - 1);
+        if ((int)blockIdx.x < kept_splits) {
+            t_begin = blockIdx.x * tiles_per_split;
+            t_end = min(kept_tiles - 1, t_begin + tiles_per_split - 1);
+        } else {
+            t_begin = kept_tiles + (blockIdx.x - kept_splits) * tiles_per_split;
+            t_end = min(t_end, t_begin + tiles_per_split - 1);
+        }
         if (t_begin > t_end) {  // nothing in this range: a maximum of -inf tells the merge to pass over it
             if (tid < rows_here) {
                 float* dst = partial + (((size_t)(q0 + row_token(tid)) * heads + row_head(tid)) * splits + blockIdx.x) * (DV + 2);
@@ -150,7 +172,7 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
             return;
         }
     }
-    load_tile(t_begin, 0);
+    load_tile(tile_of(t_begin), 0);
     // the block's queries (rows beyond the request's tokens read as zero)
     for (int i = tid; i < ROWS * (D / 8); i += THREADS) {
         int r = i / (D / 8), c = i - r * (D / 8);
@@ -176,16 +198,18 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
     // running maximum (of score * scale * log2 e) and this thread's share of the running sum; the
     // sink's term of the sum is counted by the first thread of the four that share a row
     const float sl2 = scale * LOG2E;
+    const float cap_in = softcap > 0.f ? scale / softcap : 0.f, cap_out = softcap * LOG2E;
     const bool with_sink = sinks != nullptr && !split_mode;  // (split: the merge adds the sink's term)
     float sink2 = with_sink ? sinks[head] * LOG2E : -INFINITY;
     float m_a = sink2, m_b = sink2;
     float l_a = (with_sink && t4 == 0) ? 1.f : 0.f, l_b = l_a;
 
     int buf = 0;
-    for (int t = t_begin; t <= t_end; ++t, buf ^= 1) {
+    for (int ti = t_begin; ti <= t_end; ++ti, buf ^= 1) {
+        const int t = tile_of(ti);
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();  // the tile has landed for everyone, and everyone is done with the other buffer
-        if (t < t_end) load_tile(t + 1, buf ^ 1);
+        if (ti < t_end) load_tile(tile_of(ti + 1), buf ^ 1);
         if (!active) continue;
         const __nv_bfloat16* kt = ks + (size_t)buf * KEYS * LDK;
         const __nv_bfloat16* vt = vs + (size_t)buf * KEYS * LDV;
@@ -211,8 +235,9 @@ sink_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat
             for (int e = 0; e < 4; ++e) {
                 int key_pos = kp + (e & 1);
                 int pos = e < 2 ? pos_a : pos_b, lo = e < 2 ? lo_a : lo_b;
-                bool visible = key_pos <= pos && key_pos >= lo;
-                s[nt][e] = visible ? s[nt][e] * sl2 : -INFINITY;
+                bool visible = key_pos <= pos && (key_pos >= lo || key_pos < keep_first);
+                float sc = softcap > 0.f ? cap_out * tanh_fast(s[nt][e] * cap_in) : s[nt][e] * sl2;
+                s[nt][e] = visible ? sc : -INFINITY;
             }
             mx_a = fmaxf(mx_a, fmaxf(s[nt][0], s[nt][1]));
             mx_b = fmaxf(mx_b, fmaxf(s[nt][2], s[nt][3]));
@@ -354,10 +379,12 @@ IE_API int ie_sink_attention_mma(const void* q, const void* k_cache, const void*
                                  int table_width, const int* cu_q, const int* ctx_lens, void* out, int num_seqs,
                                  int max_q_len, int heads, int kv_heads, int page_size, int total_pages,
                                  float scale, int window, const float* sinks, const float* out_gate, int gate_ld,
-                                 float* partial, int splits, int tiles_per_split, int num_tokens, int* err,
-                                 void* stream) {
+                                 float* partial, int splits, int tiles_per_split, int num_tokens, float softcap,
+                                 int keep_first, int kept_splits, int* err, void* stream) {
     if (num_seqs <= 0 || max_q_len <= 0) return 0;
     if (kv_heads <= 0 || heads % kv_heads != 0 || page_size < 1 || (page_size & (page_size - 1)) || window < 0)
+        return (int)cudaErrorInvalidValue;
+    if (softcap < 0.f || keep_first < 0 || kept_splits < 0 || (window == 0 && keep_first > 0))
         return (int)cudaErrorInvalidValue;
     size_t smem = (size_t)(ROWS * LDK + 2 * KEYS * LDK + 2 * KEYS * LDV) * sizeof(__nv_bfloat16);
     static IePerDevice allowed;
@@ -367,13 +394,13 @@ IE_API int ie_sink_attention_mma(const void* q, const void* k_cache, const void*
         // ranges of key tiles: a request's tokens times the heads of a group are one tile of rows, and
         // the scratch holds [num_tokens, heads, splits, DV + 2] floats
         if (max_q_len * (heads / kv_heads) > ROWS || splits < 1 || splits > MERGE_MAX_SPLITS || tiles_per_split < 1 ||
-            num_tokens < 1)
+            num_tokens < 1 || kept_splits >= splits)
             return (int)cudaErrorInvalidValue;
         int rc = ie_launch(sink_attention_mma_kernel, dim3(splits, kv_heads, num_seqs), dim3(THREADS), smem,
                            (cudaStream_t)stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
                            (const __nv_bfloat16*)v_cache, block_tables, table_width, cu_q, ctx_lens, (__nv_bfloat16*)out,
                            heads, kv_heads, page_size, total_pages, scale, window, sinks, out_gate, gate_ld, partial,
-                           splits, tiles_per_split, err);
+                           splits, tiles_per_split, softcap, keep_first, kept_splits, err);
         if (rc != 0) return rc;
         return ie_launch(sink_attention_merge_kernel, dim3(num_tokens * heads), dim3(128), 0, (cudaStream_t)stream,
                          (const float*)partial, cu_q, num_seqs, (__nv_bfloat16*)out, heads, splits, sinks, out_gate,
@@ -383,5 +410,5 @@ IE_API int ie_sink_attention_mma(const void* q, const void* k_cache, const void*
     return ie_launch(sink_attention_mma_kernel, grid, dim3(THREADS), smem, (cudaStream_t)stream,
                      (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_tables,
                      table_width, cu_q, ctx_lens, (__nv_bfloat16*)out, heads, kv_heads, page_size, total_pages, scale,
-                     window, sinks, out_gate, gate_ld, (float*)nullptr, 1, 0, err);
+                     window, sinks, out_gate, gate_ld, (float*)nullptr, 1, 0, softcap, keep_first, 0, err);
 }

@@ -5,7 +5,9 @@
 //    buckets, or row `buckets` for a request's first token.  The token before a step's first one is
 //    kept per request in a state slot (as the integer's bits) and moved on by the same block that
 //    read it.
-//  * sandwich_norm: y = sum of the parts of `delta` (+ bias); y <- rms(y) * post_w (if post_w);
+//  * sandwich_norm: y = sum of the parts of `delta` (+ the parts of `delta2`, the output of a second
+//    sublayer that read the same input) (+ bias) (+ the row of `extra`, a second stream of the rows'
+//    shape: the embedding's output that a looped model adds again); y <- rms(y) * post_w (if post_w);
 //    h += y; out = rms(h) * pre_w (if out).  One block per row; both sums of squares are added in
 //    an order that depends on the row's width alone.
 //  * silu_mul_bias: out = silu(g + bg) * (u + bu) from rows that hold gates, then ups (32-bit, or the
@@ -109,7 +111,8 @@ __device__ __forceinline__ void store_pack(__nv_bfloat16* p, const Pack<VEC>& r)
 template <typename OutT, int VEC>
 __global__ void __launch_bounds__(SN_THREADS)
 sandwich_norm_kernel(float* __restrict__ h, const float* __restrict__ delta, int num_partials, size_t partial_stride,
-                     const float* __restrict__ bias, const float* __restrict__ post_w, float post_eps,
+                     const float* __restrict__ delta2, int num_partials2, size_t partial_stride2,
+                     const float* __restrict__ extra, const float* __restrict__ bias, const float* __restrict__ post_w, float post_eps,
                      const float* __restrict__ pre_w, float pre_eps, OutT* __restrict__ out,
                      const int* __restrict__ rows, int hidden) {
     extern __shared__ __align__(16) float row_buf[];  // [hidden]
@@ -124,6 +127,16 @@ sandwich_norm_kernel(float* __restrict__ h, const float* __restrict__ delta, int
             Pack<VEC> y = load_pack<VEC>(delta + src + i);
             for (int p = 1; p < num_partials; ++p) {
                 Pack<VEC> d = load_pack<VEC>(delta + p * partial_stride + src + i);
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) y.v[v] += d.v[v];
+            }
+            for (int p = 0; p < num_partials2; ++p) {
+                Pack<VEC> d = load_pack<VEC>(delta2 + p * partial_stride2 + src + i);
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) y.v[v] += d.v[v];
+            }
+            if (extra) {
+                Pack<VEC> d = load_pack<VEC>(extra + src + i);
 #pragma unroll
                 for (int v = 0; v < VEC; ++v) y.v[v] += d.v[v];
             }
@@ -356,17 +369,21 @@ IE_API int ie_bigram_embedding(const void* embed, const void* bigram, int table_
 // `out` may be null (only the residual stream is brought up to date); `delta` may be null (a plain
 // norm of h); `rows` selects rows, and then h is not modified.
 IE_API int ie_sandwich_norm(float* h, const float* delta, int num_partials, long long partial_stride,
-                            const float* bias, const float* post_w, float post_eps, const float* pre_w,
+                            const float* delta2, int num_partials2, long long partial_stride2,
+                            const float* extra, const float* bias, const float* post_w, float post_eps, const float* pre_w,
                             float pre_eps, void* out, int out_dtype, const int* rows, int num_rows, int hidden,
                             void* stream) {
     if (num_rows <= 0) return 0;
     if (delta != nullptr && num_partials < 1) return (int)cudaErrorInvalidValue;
+    if (delta == nullptr && (delta2 != nullptr || extra != nullptr)) return (int)cudaErrorInvalidValue;
+    if (delta2 == nullptr) num_partials2 = 0;
     if (out != nullptr && pre_w == nullptr) return (int)cudaErrorInvalidValue;
     size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
-    bool vec = hidden % 4 == 0 && (size_t)partial_stride % 4 == 0 &&
+    bool vec = hidden % 4 == 0 && (size_t)partial_stride % 4 == 0 && (size_t)partial_stride2 % 4 == 0 &&
                ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(bias) |
+                 reinterpret_cast<uintptr_t>(delta2) | reinterpret_cast<uintptr_t>(extra) |
                  reinterpret_cast<uintptr_t>(post_w) | reinterpret_cast<uintptr_t>(pre_w) |
                  reinterpret_cast<uintptr_t>(out)) % 16 == 0);
 #define IE_SN_LAUNCH(T, V)                                                                                         \
@@ -377,8 +394,8 @@ IE_API int ie_sandwich_norm(float* h, const float* delta, int num_partials, long
             if (e != cudaSuccess) return (int)e;                                                                   \
         }                                                                                                          \
         return ie_launch(sandwich_norm_kernel<T, V>, dim3(num_rows), dim3(SN_THREADS), smem, s, h, delta,          \
-                         num_partials, (size_t)partial_stride, bias, post_w, post_eps, pre_w, pre_eps, (T*)out,    \
-                         rows, hidden);                                                                            \
+                         num_partials, (size_t)partial_stride, delta2, num_partials2, (size_t)partial_stride2,     \
+                         extra, bias, post_w, post_eps, pre_w, pre_eps, (T*)out, rows, hidden);                    \
     } while (0)
     if (out_dtype == IE_BF16) {
         if (vec) IE_SN_LAUNCH(__nv_bfloat16, 4);

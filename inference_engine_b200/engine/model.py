@@ -118,7 +118,8 @@ class Model:
             self.bindings.append(assign(req))
         ask = getattr(self.embedding, "cache_request", None)
         self.embedding_binding = assign(ask()) if ask is not None else None
-        self.paged_groups = [PagedGroupSpec(n, r.num_kv_heads, r.head_dim, r.window, r.value_dim, r.chunk)
+        self.paged_groups = [PagedGroupSpec(n, r.num_kv_heads, r.head_dim, r.window, r.value_dim, r.chunk,
+                                            r.keep_first)
                              for r, n in paged]
         self.state_groups = [StateGroupSpec(n, tuple(r.shape)) for r, n in state]
         # Context groups are listed paged first, then state: remap the negative indices.
@@ -166,11 +167,20 @@ class Model:
         for entry, binding in zip(self.spec.schedule, self.bindings):
             block = self.blocks[entry.layer]
             if entry.before is not None:
-                # the stream part sees the whole stream: what is pending is added first
-                if delta is not None:
-                    self._settle(h, delta, scale, post, ctx)
-                    delta, scale, post = None, 1.0, None
-                self.stream_parts[entry.before].forward(h, x0, ctx)
+                part = self.stream_parts[entry.before]
+                # a stream part that only adds something to the stream joins the pending add (and the
+                # next norm's kernel) where it can
+                folded = None
+                if delta is not None and scale == 1.0 and hasattr(part, "fold"):
+                    folded = part.fold(post, x0)
+                if folded is not None:
+                    post = folded
+                else:
+                    # the stream part sees the whole stream: what is pending is added first
+                    if delta is not None:
+                        self._settle(h, delta, scale, post, ctx)
+                        delta, scale, post = None, 1.0, None
+                    part.forward(h, x0, ctx)
             if post is None:
                 delta = block.forward(h, delta, ctx, binding, delta_scale=scale)
             else:

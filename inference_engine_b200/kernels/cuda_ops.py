@@ -217,10 +217,11 @@ class CudaOps:
             "ie_gemm_tma_bf16": [P, P, P, I, I, I, I, I, I, P, P],
             "ie_gemm_tc5_bf16": [P, P, P, I, I, I, I, I, I, P, P],
             "ie_gemm_tc5_ok": [I, I, I],
-            "ie_paged_attention_generic": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P, P, I, P, P],
+            "ie_paged_attention_generic": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P, P, I, F, I, P, P],
             "ie_sample": [P, I, I, P, P, P, P, P, P, I, P, P, P, P, P],
             "ie_bigram_embedding": [P, P, I, P, P, P, P, P, P, L, I, P, I, I, I, I, L, L, P, P],
-            "ie_sandwich_norm": [P, P, I, L, P, P, F, P, F, P, I, P, I, I, P],
+            "ie_sandwich_norm": [P, P, I, L, P, I, L, P, P, P, F, P, F, P, I, P, I, I, P],
+            "ie_scale_softcap": [P, F, F, L, P],
             "ie_silu_mul_bias": [P, I, P, P, I, I, I, P],
             "ie_concat_cast": [P, P, P, I, I, I, P],
             "ie_weighted_sum": [P, F, P, F, P, L, P],
@@ -353,6 +354,12 @@ class CudaOps:
     def scale_(self, t, factor: float) -> None:
         """``t *= factor`` for a contiguous 32-bit tensor."""
         self._check(self._scale(t.data_ptr(), float(factor), t.numel(), self._stream()), "scale")
+
+    @_kind("head")
+    def scale_softcap_(self, t, factor: float, cap: float) -> None:
+        """``t <- cap * tanh(t * factor / cap)`` for a contiguous 32-bit tensor."""
+        self._check(self._scale_softcap(t.data_ptr(), float(factor), float(cap), t.numel(), self._stream()),
+                    "scale_softcap")
 
     FEW_ROWS = 16  # up to this many rows a bfloat16 product runs the weight-streaming kernel
 
@@ -870,7 +877,7 @@ class CudaOps:
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q),
             block_tables.data_ptr(), block_tables.shape[1], ctx.seq_of_token.data_ptr(),
             ctx.positions.data_ptr(), out.data_ptr(), ctx.num_tokens, nh, nkv, hd, hd, hd, page_size,
-            k_cache.shape[0], scale, window, 0, None, None, None, 0, self._err_ptr, self._stream()), "paged_attention")
+            k_cache.shape[0], scale, window, 0, None, None, None, 0, 0.0, 0, self._err_ptr, self._stream()), "paged_attention")
 
     @_kind("attention.latent")
     def latent_paged_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, value_dim,
@@ -905,8 +912,8 @@ class CudaOps:
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q),
             block_tables.data_ptr(), block_tables.shape[1], ctx.seq_of_token.data_ptr(),
             ctx.positions.data_ptr(), out.data_ptr(), ctx.num_tokens, nh, nkv, hd, value_dim,
-            v_cache.shape[-1], page_size, k_cache.shape[0], scale, window, 0, None, None, None, 0, self._err_ptr,
-            self._stream()), "paged_attention_latent")
+            v_cache.shape[-1], page_size, k_cache.shape[0], scale, window, 0, None, None, None, 0, 0.0, 0,
+            self._err_ptr, self._stream()), "paged_attention_latent")
 
     # --- kernels of single mixers and feed-forwards (libraries built on first use) -------------
 
@@ -925,7 +932,7 @@ class CudaOps:
             "ie_gated_rms_heads": "P P F P P I L I P",
         },
         "routed": {
-            "ie_route_topk": "P I P P I I I I I I P P P",
+            "ie_route_topk": "P I P P I I I I I I I P I F P P P",
             "ie_routed_max_tiles": "I I",
             "ie_routed_align": "P I I P P P I P",
             "ie_routed_gate_up": "P P P I P P P I I I I F I F F P",
@@ -940,7 +947,7 @@ class CudaOps:
             "ie_lowrank_decay": "P I P P F P I I I P",
         },
         "gated_attn": {
-            "ie_qk_norm_rope_write": "P I P P I I P I P P F P P P I P I I I I I I I P P",
+            "ie_qk_norm_rope_write": "P I P P I I P I I I P P F P P P I P I I I I I I I P P",
         },
     }
 
@@ -1037,12 +1044,21 @@ class CudaOps:
             o.shape[0] * heads, vdim, self._stream()), "gated_rms_heads")
 
     @_kind("routed.route")
-    def route_topk(self, x, w_router, groups, keep, ids, weights, bias=None) -> None:
+    def route_topk(self, x, w_router, groups, keep, ids, weights, bias=None, scoring: str = "softmax",
+                   correction=None, group_top: int = 1, weight_scale: float = 1.0) -> None:
         """Softmax scores (of the router's logits plus ``bias``, if given), group limit and the ``top``
-        experts per token with their normalised weights."""
+        experts per token with their normalised weights, times ``weight_scale``.  ``scoring="sigmoid"``:
+        the scores are the logits' sigmoids; ``correction`` (one number per expert) is added to them
+        for the choice of groups and experts only, and a group's score is the sum of its
+        ``group_top`` (1 or 2) largest choice scores."""
+        if scoring not in ("softmax", "sigmoid"):
+            raise KernelError(f"route_topk: no scoring {scoring!r}")
+        if correction is not None and (correction.dtype != self.torch.float32 or correction.numel() != w_router.shape[0]):
+            raise KernelError("route_topk: the correction is one 32-bit number per expert")
         self._check(self._part_lib("routed").ie_route_topk(
             x.data_ptr(), _dtype_code(x), w_router.data_ptr(), self._ptr(bias), x.shape[0], x.shape[1], w_router.shape[0],
-            ids.shape[1], groups, keep, ids.data_ptr(), weights.data_ptr(), self._stream()), "route_topk")
+            ids.shape[1], groups, keep, 1 if scoring == "sigmoid" else 0, self._ptr(correction), int(group_top),
+            float(weight_scale), ids.data_ptr(), weights.data_ptr(), self._stream()), "route_topk")
 
     def routed_experts(self, x, ids, weights, w_gate_up, w_down, *, limit, alpha, up_offset, ws, tag="moe"):
         """The chosen experts' weighted outputs as ``[top, N, hidden]`` 32-bit slices (to be added in
@@ -1103,13 +1119,21 @@ class CudaOps:
             mul_cur, self._err_ptr, self._stream()), "bigram_embedding")
 
     @_kind("norm")
-    def sandwich_norm(self, h, delta, bias, post_weight, post_eps, weight, eps, out, rows=None) -> None:
-        """``y = delta (+ bias)``; ``y <- rms(y) * post_weight`` if given; ``h += y`` (not with
-        ``rows``); ``out = rms(h) * weight`` unless ``out`` is None.  ``delta`` may be None."""
+    def sandwich_norm(self, h, delta, bias, post_weight, post_eps, weight, eps, out, rows=None, second=None,
+                      extra=None) -> None:
+        """``y = delta (+ second) (+ bias) (+ extra)``; ``y <- rms(y) * post_weight`` if given; ``h += y``
+        (not with ``rows``); ``out = rms(h) * weight`` unless ``out`` is None.  ``delta`` may be None.
+        ``second``: another sublayer's output, whole or in parts like ``delta``; ``extra``: a 32-bit array
+        of the stream's shape, added row by row."""
         n = h.shape[0] if rows is None else rows.shape[0]
         parts, stride = self._partials(delta)
+        parts2, stride2 = self._partials(second)
+        if extra is not None and (extra.dtype != self.torch.float32 or tuple(extra.shape) != tuple(h.shape)
+                                  or not extra.is_contiguous()):
+            raise KernelError("sandwich_norm: the extra rows must be a 32-bit array like the stream")
         self._check(self._sandwich_norm(
-            h.data_ptr(), self._ptr(delta), parts, stride, self._ptr(bias), self._ptr(post_weight), post_eps,
+            h.data_ptr(), self._ptr(delta), parts, stride, self._ptr(second), parts2 if second is not None else 0,
+            stride2, self._ptr(extra), self._ptr(bias), self._ptr(post_weight), post_eps,
             self._ptr(weight), eps, self._ptr(out), _dtype_code(out) if out is not None else 0, self._ptr(rows), n,
             h.shape[1], self._stream()), "sandwich_norm")
 
@@ -1242,14 +1266,20 @@ class CudaOps:
     @_kind("rotary+cache")
     def qk_norm_rope_write(self, proj, positions, table, rot_dims, q_weight, k_weight, eps, q_out, k_cache,
                            v_cache, slot_mapping, heads, kv_heads, dim, vdim, page_size, bias=None,
-                           value_norm: bool = False) -> None:
+                           value_norm: bool = False, values_from_keys: bool = False,
+                           interleaved: bool = False) -> None:
         """The input stage of an attention with per-head norms (see ``csrc/gated_attention.cu``).
         ``q_weight`` / ``k_weight`` None: queries and keys are not normalised; ``bias``: one row laid
         out like the projection's first columns, added first; ``value_norm``: value heads are divided
-        by their root mean square.  ``proj`` may hold more columns behind the values."""
+        by their root mean square.  ``proj`` may hold more columns behind the values.
+        ``values_from_keys``: the projection holds queries and keys only, and the cached values are
+        the keys as projected (with their bias, before any norm or rotation).  ``interleaved``: the
+        rotation pairs entry ``2i`` with ``2i + 1`` instead of ``i`` with ``i + rot_dims / 2``."""
         if table is not None and table.shape[2] * 2 != rot_dims:
             raise KernelError("rotary table does not match the rotated dims")
-        need = (heads + kv_heads) * dim + kv_heads * vdim
+        if values_from_keys and vdim != dim:
+            raise KernelError("values that are the keys have the keys' size")
+        need = (heads + kv_heads) * dim + (0 if values_from_keys else kv_heads * vdim)
         if proj.dtype != self.torch.float32 or proj.shape[1] < need or (q_weight is None) != (k_weight is None):
             raise KernelError("qk_norm_rope_write reads the fused 32-bit projection of queries, keys and values")
         if bias is not None and (bias.dtype != self.torch.float32 or bias.numel() < need):
@@ -1257,6 +1287,7 @@ class CudaOps:
         self._check(self._part_lib("gated_attn").ie_qk_norm_rope_write(
             proj.data_ptr(), proj.stride(0), positions.data_ptr(), self._ptr(table), rot_dims,
             0 if table is None else table.shape[0], self._ptr(bias), 1 if value_norm else 0,
+            1 if values_from_keys else 0, 1 if interleaved else 0,
             self._ptr(q_weight), self._ptr(k_weight), eps, q_out.data_ptr(),
             k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q_out), self._ptr(slot_mapping), proj.shape[0],
             heads, kv_heads, dim, vdim, page_size, k_cache.shape[0], self._err_ptr, self._stream()),
@@ -1301,7 +1332,7 @@ class CudaOps:
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q),
             block_tables.data_ptr(), block_tables.shape[1], ctx.seq_of_token.data_ptr(),
             ctx.positions.data_ptr(), out.data_ptr(), ctx.num_tokens, nh, nkv, hd, vdim, vdim, page_size,
-            k_cache.shape[0], scale, 0, int(chunk or 0), head_bias.data_ptr(), None, None, 0, self._err_ptr,
+            k_cache.shape[0], scale, 0, int(chunk or 0), head_bias.data_ptr(), None, None, 0, 0.0, 0, self._err_ptr,
             self._stream()), "sigmoid_attention")
 
     def _sink_attention_lib(self, hd: int, vdim: int):
@@ -1314,7 +1345,7 @@ class CudaOps:
                 raise KernelError(f"the kernel library {path} could not be loaded: {exc}") from exc
             P, I, F = c_void_p, c_int, c_float
             lib.ie_sink_attention_mma.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P, I, P, I, I, I,
-                                                  P, P]
+                                                  F, I, I, P, P]
             lib.ie_sink_attention_mma.restype = c_int
             self._sinkattn_libs[(hd, vdim)] = lib
         return lib
@@ -1325,7 +1356,7 @@ class CudaOps:
 
     @_kind("attention.sink")
     def sink_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, vdim, page_size, scale,
-                       window, sinks, gate, out) -> None:
+                       window, sinks, gate, out, softcap: float | None = None, keep_first: int = 0) -> None:
         """Softmax attention over the paged cache whose denominator also holds ``exp(sinks[head])`` (a
         term without key or value; ``sinks`` None: a plain softmax), over the latest ``window``
         positions (None or 0: all), with value rows of ``vdim`` entries; ``gate`` (a 32-bit view
@@ -1337,21 +1368,30 @@ class CudaOps:
         window, the window's key tiles are cut among blocks and merged by a second kernel, so a
         decoded token's sums are the same numbers in another order than in a step that also holds
         a prompt portion); 32-bit and other sizes the general kernel, whose order of operations
-        does not depend on the batch."""
+        does not depend on the batch.  ``softcap``: a score ``s`` becomes ``softcap * tanh(s / softcap)``
+        before the softmax.  ``keep_first`` (with a window): the keys at positions below it stay visible
+        to every later query beside its window, at their own positions."""
         if gate is not None and (gate.dtype != self.torch.float32 or gate.stride(1) != 1):
             raise KernelError("sink_attention: the output gate must be a 32-bit view with unit stride")
+        cap = float(softcap or 0.0)
+        keep = int(keep_first or 0) if window else 0
+        if cap < 0 or keep < 0:
+            raise KernelError("sink_attention: the cap of the scores and the kept keys cannot be negative")
         if (self.sink_mma and q.dtype == self.torch.bfloat16 and hd % 16 == 0 and vdim % 16 == 0
                 and 16 <= hd <= 256 and 16 <= vdim <= 256 and page_size & (page_size - 1) == 0):
             lib = self._sink_attention_lib(hd, vdim)
             bounds = getattr(ctx, "bounds", None)
             longest = bounds[0] if bounds is not None else ctx.max_q_len  # (a captured step: its token bound)
-            scratch, splits, per_split = None, 1, 0
+            scratch, splits, per_split, kept_splits = None, 1, 0, 0
             if window and longest <= self.SINK_SPLIT_ROWS and longest * (nh // nkv) <= 64:
                 # the tiles between the first row's oldest key and the last row's own position, in
-                # ranges of two: from the window and the row bound alone, so a captured launch stays valid
+                # ranges of two: from the window and the row bound alone, so a captured launch stays valid;
+                # the tiles of the kept first keys are ranges of their own in front of them
                 tiles = (int(window) + longest - 2) // 64 + 2
-                per_split = max(2, -(-tiles // 1024))  # (the merge kernel takes up to 1,024 ranges)
-                splits = -(-tiles // per_split)
+                kept_tiles = -(-keep // 64)
+                per_split = max(2, -(-(tiles + kept_tiles) // 1022))  # (the merge kernel takes up to 1,024 ranges)
+                kept_splits = -(-kept_tiles // per_split)
+                splits = -(-tiles // per_split) + kept_splits
                 if splits > 1:
                     scratch = self._scratch(ctx, "attn.sink_partial", ctx.num_tokens * nh * splits * (vdim + 2), q.device)
             self._check(lib.ie_sink_attention_mma(
@@ -1359,7 +1399,8 @@ class CudaOps:
                 block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(), ctx.num_seqs,
                 longest, nh, nkv, page_size, k_cache.shape[0], scale, int(window or 0), self._ptr(sinks),
                 self._ptr(gate), 0 if gate is None else gate.stride(0), self._ptr(scratch), splits, per_split,
-                ctx.num_tokens, self._err_ptr, self._stream()), "sink_attention_mma")
+                ctx.num_tokens, cap, keep, kept_splits if scratch is not None else 0, self._err_ptr, self._stream()),
+                "sink_attention_mma")
             if scratch is not None:  # (the call launched the merge kernel too)
                 self.launches += 1
                 self.launch_counts["sink_attention_merge"] = self.launch_counts.get("sink_attention_merge", 0) + 1
@@ -1369,7 +1410,7 @@ class CudaOps:
             block_tables.data_ptr(), block_tables.shape[1], ctx.seq_of_token.data_ptr(),
             ctx.positions.data_ptr(), out.data_ptr(), ctx.num_tokens, nh, nkv, hd, vdim, vdim, page_size,
             k_cache.shape[0], scale, int(window or 0), 0, None, self._ptr(sinks), self._ptr(gate),
-            0 if gate is None else gate.stride(0), self._err_ptr, self._stream()), "sink_attention")
+            0 if gate is None else gate.stride(0), cap, keep, self._err_ptr, self._stream()), "sink_attention")
 
     @_kind("activation")
     def silu_mul(self, gate_up, out, interleave: int = 0) -> None:

@@ -67,6 +67,9 @@ class PagedKVRequest:
     # A query sees only the keys of its own chunk of this many positions, counted from position 0
     # (``None`` = no chunks): pages that lie wholly before the current chunk are given back.
     chunk: int | None = None
+    # With a window: the first ``keep_first`` positions stay visible to every later query, so the
+    # pages that hold them are never given back while the request lives.
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)

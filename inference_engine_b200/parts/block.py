@@ -18,6 +18,11 @@ the stream: ``x <- x + sigmoid(W1 h + b1) * mixer(h)`` with ``h = norm(x)``, the
 the compute dtype with 32-bit sums; sigmoid, multiplication and add are 32-bit and sit in the
 kernel of the next norm (the pending delta travels with its gate: ``output_post``).  A mixer or
 feed-forward that starts with one product over its input carries its gate's rows in that product.
+
+``parallel_residual``: one norm, and both sublayers read its output: ``x <- x + mixer(h) +
+feed_forward(h)`` with ``h = norm(x)``.  The two outputs stay apart (each whole or in the parts of a
+split product) and are added, with the mixer's output bias if it has one, in the kernel of the
+next norm: the mixer's output is the pending delta, the rest travels beside it (``output_post``).
 """
 
 from __future__ import annotations
@@ -25,13 +30,21 @@ from __future__ import annotations
 import os
 
 from .base import Block, BuildEnv, CacheBinding, WeightDecl
-from .norm import PostNorm, ResidualGate
+from .norm import AddedTerms, PostNorm, ResidualGate
 from .registry import build_part, register_part
+
+
+def _adds_no_output_bias(mixer) -> None:
+    """An arrangement that adds the mixer's output as it is cannot take a mixer that leaves its
+    output bias to the add."""
+    if getattr(mixer, "names", None) and mixer.names.get("o_bias"):
+        raise ValueError("this arrangement of a layer does not add a mixer's output bias")
 
 
 @register_part("block", "prenorm_residual")
 class PreNormResidualBlock(Block):
     def __init__(self, mixer, feed_forward, pre_mixer, pre_feed_forward, residual_mult: float = 1.0) -> None:
+        _adds_no_output_bias(mixer)
         self.mixer, self.feed_forward = mixer, feed_forward
         self.pre_mixer, self.pre_feed_forward = pre_mixer, pre_feed_forward
         self.residual_mult = float(residual_mult)
@@ -60,6 +73,43 @@ class PreNormResidualBlock(Block):
         return self.feed_forward.forward(x, ctx)
 
 
+@register_part("block", "parallel_residual")
+class ParallelResidualBlock(Block):
+    """The norm ``pre_mixer`` feeds the mixer and the feed-forward alike.  A mixer with an output
+    bias leaves it to the add (``output_bias``)."""
+
+    def __init__(self, mixer, feed_forward, pre_mixer) -> None:
+        self.mixer, self.feed_forward, self.pre_mixer = mixer, feed_forward, pre_mixer
+        self.residual_mult = 1.0
+        self._pending: AddedTerms | None = None
+
+    @classmethod
+    def from_spec(cls, params: dict, env: BuildEnv, *, layer, **_):
+        return cls(build_part("mixer", layer.mixer, env),
+                   build_part("feed_forward", layer.feed_forward, env) if layer.feed_forward is not None else None,
+                   build_part("norm", layer.norms["pre_mixer"], env))
+
+    def parts(self):
+        return [p for p in (self.pre_mixer, self.mixer, self.feed_forward) if p is not None]
+
+    @property
+    def output_post(self) -> AddedTerms | None:
+        """What is added together with the delta this block's last forward left pending."""
+        return self._pending
+
+    def forward(self, h, delta, ctx, binding: CacheBinding | None, delta_scale: float = 1.0, delta_post=None):
+        if delta_post is None:
+            x = self.pre_mixer.add_norm(h, delta, ctx, tag="norm.mixer", delta_scale=delta_scale)
+        else:
+            x = self.pre_mixer.add_norm(h, delta, ctx, tag="norm.mixer", delta_scale=delta_scale,
+                                        delta_post=delta_post)
+        mixed = self.mixer.forward(x, ctx, binding)
+        fed = self.feed_forward.forward(x, ctx) if self.feed_forward is not None else None
+        bias = getattr(self.mixer, "output_bias", None)
+        self._pending = AddedTerms(bias, fed) if (bias is not None or fed is not None) else None
+        return mixed
+
+
 @register_part("block", "sandwich_residual")
 class SandwichResidualBlock(Block):
     """Norms ``pre_mixer``, ``post_mixer`` and, with a feed-forward, ``pre_feed_forward`` and
@@ -67,6 +117,7 @@ class SandwichResidualBlock(Block):
     (``output_bias``)."""
 
     def __init__(self, mixer, feed_forward, norms: dict) -> None:
+        _adds_no_output_bias(mixer)
         self.mixer, self.feed_forward, self.norms = mixer, feed_forward, norms
         self.residual_mult = 1.0
 
@@ -105,6 +156,7 @@ class GatedPreNormResidualBlock(Block):
     bias name may be absent)."""
 
     def __init__(self, mixer, feed_forward, pre_mixer, pre_feed_forward, names: dict, hidden_size: int, dtype) -> None:
+        _adds_no_output_bias(mixer)
         self.mixer, self.feed_forward = mixer, feed_forward
         self.pre_mixer, self.pre_feed_forward = pre_mixer, pre_feed_forward
         self.names, self.hidden_size, self.dtype = dict(names), int(hidden_size), dtype

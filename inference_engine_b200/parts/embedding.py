@@ -90,16 +90,20 @@ class LinearHead(Part):
     category = "head"
 
     def __init__(self, weight: str | None, vocab_size: int, hidden_size: int, dtype,
-                 logit_scale: float = 1.0) -> None:
+                 logit_scale: float = 1.0, softcap: float | None = None) -> None:
         self.weight_name, self.vocab_size, self.hidden_size = weight, vocab_size, hidden_size
         self.dtype, self.weight = dtype, None
         self.logit_scale = float(logit_scale)  # the 32-bit logits are multiplied by it
+        # ... and then squashed into (-softcap, softcap): c * tanh(logits / c), if the model caps them
+        self.softcap = None if not softcap else float(softcap)
+        if self.softcap is not None and not self.softcap > 0:
+            raise ValueError("the cap of the logits must be positive")
 
     @classmethod
     def from_spec(cls, params: dict, env: BuildEnv, **_):
         # weight=None means tied: the model hands over the embedding table at bind time.
         return cls(params.get("weight"), params["vocab_size"], env.hidden_size, env.torch_dtype,
-                   params.get("logit_scale", 1.0))
+                   params.get("logit_scale", 1.0), params.get("softcap"))
 
     def weights(self) -> dict[str, WeightDecl]:
         if self.weight_name is None:
@@ -118,6 +122,8 @@ class LinearHead(Part):
 
         logits = ctx.ws.buffer("logits", x.shape[0], self.vocab_size, torch.float32, rows_cap=None)
         ctx.ops.linear(x, self.weight, logits, tag="head")
-        if self.logit_scale != 1.0:
+        if self.softcap is not None:
+            ctx.ops.scale_softcap_(logits, self.logit_scale, self.softcap)
+        elif self.logit_scale != 1.0:
             ctx.ops.scale_(logits, self.logit_scale)
         return logits

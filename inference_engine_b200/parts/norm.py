@@ -66,6 +66,30 @@ class PostNorm:
         ctx.ops.sandwich_norm(h, delta, self.bias, self.norm.weight, self.norm.eps, None, 0.0, None)
 
 
+class AddedTerms:
+    """What enters the residual stream together with a pending delta, in the same add: the output of
+    a second sublayer that read the same input (``second``: whole, or in parts like a delta), a bias
+    row of the sublayer that left the delta (``bias``), and a second stream of the rows' shape
+    (``rows_like_stream``: the embedding's output that a looped model adds again before a pass).
+    ``h += delta + second + bias + rows_like_stream`` and the next norm are one kernel."""
+
+    def __init__(self, bias=None, second=None, rows_like_stream=None) -> None:
+        self.bias, self.second, self.rows_like_stream = bias, second, rows_like_stream
+
+    def with_stream_rows(self, x0) -> "AddedTerms":
+        if self.rows_like_stream is not None:
+            raise ValueError("one second stream per add")
+        return AddedTerms(self.bias, self.second, x0)
+
+    def add_norm(self, h, delta, ctx, weight, eps, out, rows) -> None:
+        ctx.ops.sandwich_norm(h, delta, self.bias, None, 0.0, weight, eps, out, rows, second=self.second,
+                              extra=self.rows_like_stream)
+
+    def settle(self, h, delta, ctx) -> None:
+        ctx.ops.sandwich_norm(h, delta, self.bias, None, 0.0, None, 0.0, None, second=self.second,
+                              extra=self.rows_like_stream)
+
+
 class ResidualGate:
     """A sublayer's output enters the residual stream through a gate: ``h += sigmoid(gate_pre + bias) *
     delta`` element by element.  ``gate_pre`` is the 32-bit pre-activation ``[N, hidden]`` of this

@@ -6,6 +6,10 @@ router has one: ``router_bias``), in 32-bit.  The experts form
 ``keep_groups`` best groups can be chosen (``groups = keep_groups = 1``: no such limit).  The
 ``top`` allowed experts with the largest scores are taken, and their scores, divided by their sum
 (+ 1e-20), weigh the experts' outputs (without groups this is the softmax over the chosen logits).
+``scoring="sigmoid"``: a score is the sigmoid of the expert's logit; a ``correction`` per expert (a
+tensor, if named) is added to the scores for the choice of groups and experts alone, a group's score
+is the sum of its ``group_top`` largest choice scores, and the weights are the chosen experts' plain
+scores over their sum.  ``weight_scale`` multiplies the weights.
 
 An expert: ``g = min(gate(x), limit)``, ``u = clamp(up(x), -limit, limit)``,
 ``y = g * sigmoid(alpha * g) * (u + up_offset)``, output ``down(y)``; no biases.  ``limit``,
@@ -28,15 +32,24 @@ from .registry import register_part
 class RoutedExperts(FeedForward):
     def __init__(self, *, router: str, expert_prefix: str, experts: int, top: int, groups: int,
                  keep_groups: int, hidden_size: int, intermediate_size: int, limit: float | None,
-                 alpha: float, up_offset: float, dtype, router_bias: str | None = None) -> None:
+                 alpha: float, up_offset: float, dtype, router_bias: str | None = None, scoring: str = "softmax",
+                 correction: str | None = None, group_top: int = 1, weight_scale: float = 1.0) -> None:
         if not 1 <= top <= experts:
             raise ValueError(f"top ({top}) must be between 1 and the number of experts ({experts})")
         if groups < 1 or experts % groups or not 1 <= keep_groups <= groups:
             raise ValueError(f"{experts} experts cannot form {groups} equal groups of which {keep_groups} are kept")
         if top > keep_groups * (experts // groups):
             raise ValueError(f"top ({top}) exceeds the experts of the {keep_groups} kept groups")
+        if scoring not in ("softmax", "sigmoid"):
+            raise ValueError(f"scores are a 'softmax' or 'sigmoid' of the router's logits, not {scoring!r}")
+        if scoring == "softmax" and (correction is not None or group_top != 1):
+            raise ValueError("a correction of the choice and groups scored by several experts go with sigmoid scores")
+        if group_top not in (1, 2):
+            raise ValueError("a group is scored by its best expert or by its best two")
         self.router_name, self.expert_prefix, self.router_bias_name = router, expert_prefix, router_bias
         self.router_bias = None
+        self.scoring, self.correction_name, self.correction = scoring, correction, None
+        self.group_top, self.weight_scale = int(group_top), float(weight_scale)
         self.experts, self.top, self.groups, self.keep_groups = experts, top, groups, keep_groups
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.limit = None if limit is None else float(limit)
@@ -51,7 +64,9 @@ class RoutedExperts(FeedForward):
                    hidden_size=params.get("hidden_size", env.hidden_size),
                    intermediate_size=params["intermediate_size"], limit=params.get("limit"),
                    alpha=params.get("alpha", 1.702), up_offset=params.get("up_offset", 1.0),
-                   dtype=env.torch_dtype, router_bias=params.get("router_bias"))
+                   dtype=env.torch_dtype, router_bias=params.get("router_bias"),
+                   scoring=params.get("scoring", "softmax"), correction=params.get("correction"),
+                   group_top=params.get("group_top", 1), weight_scale=params.get("weight_scale", 1.0))
 
     def _name(self, e: int, which: str) -> str:
         return f"{self.expert_prefix}{e}.{which}"
@@ -61,6 +76,8 @@ class RoutedExperts(FeedForward):
         out = {self.router_name: WeightDecl((self.experts, h), "vector")}
         if self.router_bias_name is not None:
             out[self.router_bias_name] = WeightDecl((self.experts,), "vector")
+        if self.correction_name is not None:
+            out[self.correction_name] = WeightDecl((self.experts,), "vector")
         for e in range(self.experts):
             out[self._name(e, "gate")] = WeightDecl((i, h))
             out[self._name(e, "up")] = WeightDecl((i, h))
@@ -73,6 +90,8 @@ class RoutedExperts(FeedForward):
         self.w_router = tensors[self.router_name].float().contiguous()  # routing is 32-bit
         if self.router_bias_name is not None:
             self.router_bias = tensors[self.router_bias_name].float().contiguous()
+        if self.correction_name is not None:
+            self.correction = tensors[self.correction_name].float().contiguous()
         self.w_gate_up = torch.stack([
             torch.stack([tensors[self._name(e, "gate")].to(self.dtype), tensors[self._name(e, "up")].to(self.dtype)])
             for e in range(self.experts)]).contiguous()
@@ -85,7 +104,11 @@ class RoutedExperts(FeedForward):
         n = x.shape[0]
         ids = ctx.ws.buffer("moe.ids", n, self.top, torch.int32)
         weights = ctx.ws.buffer("moe.weights", n, self.top, torch.float32)
-        if self.router_bias is None:
+        if self.scoring != "softmax" or self.weight_scale != 1.0:
+            ctx.ops.route_topk(x, self.w_router, self.groups, self.keep_groups, ids, weights, bias=self.router_bias,
+                               scoring=self.scoring, correction=self.correction, group_top=self.group_top,
+                               weight_scale=self.weight_scale)
+        elif self.router_bias is None:
             ctx.ops.route_topk(x, self.w_router, self.groups, self.keep_groups, ids, weights)
         else:
             ctx.ops.route_topk(x, self.w_router, self.groups, self.keep_groups, ids, weights, bias=self.router_bias)

@@ -49,6 +49,9 @@ class RefOps:
     def scale_(self, t, factor):
         t.mul_(factor)
 
+    def scale_softcap_(self, t, factor, cap):
+        t.copy_(cap * torch.tanh(t * factor / cap))
+
     # --- latent attention ---------------------------------------------------------------------
 
     def latent_prep(self, proj, positions, table, rot_dims, norm_w, eps, q_plain, q_abs, gate, cache,
@@ -141,9 +144,25 @@ class RefOps:
 
     # --- routed experts -----------------------------------------------------------------------
 
-    def route_topk(self, x, w_router, groups, keep, ids, weights, bias=None):
+    def route_topk(self, x, w_router, groups, keep, ids, weights, bias=None, scoring="softmax", correction=None,
+                   group_top=1, weight_scale=1.0):
         n, experts, top = x.shape[0], w_router.shape[0], ids.shape[1]
         logits = x.float() @ w_router.t()
+        if scoring == "sigmoid":
+            s = torch.sigmoid(logits if bias is None else logits + bias)
+            choice = s if correction is None else s + correction
+            per = experts // groups
+            if keep < groups:
+                score = choice.view(n, groups, per).topk(min(group_top, per), dim=-1).values.sum(-1)
+                allowed = torch.zeros(n, groups, dtype=torch.bool)
+                allowed.scatter_(1, score.topk(keep, dim=-1).indices, True)
+                allowed = allowed[:, :, None].expand(-1, -1, per).reshape(n, experts)
+                choice = choice.masked_fill(~allowed, float("-inf"))
+            chosen = choice.topk(top, dim=-1).indices
+            w = s.gather(1, chosen)
+            ids.copy_(chosen.to(ids.dtype))
+            weights.copy_(w / (w.sum(-1, keepdim=True) + 1e-20) * weight_scale)
+            return
         s = (logits if bias is None else logits + bias).softmax(-1)
         per = experts // groups
         best = s.view(n, groups, per).max(-1).values
@@ -153,7 +172,7 @@ class RefOps:
         chosen = s.masked_fill(~allowed, -1.0).topk(top, dim=-1).indices
         w = s.gather(1, chosen)
         ids.copy_(chosen.to(ids.dtype))
-        weights.copy_(w / (w.sum(-1, keepdim=True) + 1e-20))
+        weights.copy_(w / (w.sum(-1, keepdim=True) + 1e-20) * weight_scale)
 
     def routed_experts(self, x, ids, weights, w_gate_up, w_down, *, limit, alpha, up_offset, ws, tag="moe"):
         n, top = ids.shape
@@ -190,10 +209,15 @@ class RefOps:
         if real < ids.shape[0]:  # the padding of a fixed-size launch: position 0
             out[real:] = embed[ids[real:].long()].float() + bigram[buckets].float()
 
-    def sandwich_norm(self, h, delta, bias, post_weight, post_eps, weight, eps, out, rows=None):
+    def sandwich_norm(self, h, delta, bias, post_weight, post_eps, weight, eps, out, rows=None, second=None,
+                      extra=None):
         x = h if rows is None else h[rows.long()]
         if delta is not None:
             y = delta.sum(0) if delta.dim() == 3 else delta
+            if second is not None:
+                y = y + (second.sum(0) if second.dim() == 3 else second)
+            if extra is not None:
+                y = y + extra
             if rows is not None:
                 y = y[rows.long()]
             if bias is not None:
@@ -301,15 +325,15 @@ class RefOps:
 
     def qk_norm_rope_write(self, proj, positions, table, rot_dims, q_weight, k_weight, eps, q_out, k_cache,
                            v_cache, slot_mapping, heads, kv_heads, dim, vdim, page_size, bias=None,
-                           value_norm=False):
+                           value_norm=False, values_from_keys=False, interleaved=False):
         n = proj.shape[0]
-        end = (heads + kv_heads) * dim + kv_heads * vdim
+        end = (heads + kv_heads) * dim + (0 if values_from_keys else kv_heads * vdim)
         proj = proj[:, :end].float()
         if bias is not None:
             proj = proj + bias[:end]
         q = proj[:, : heads * dim].reshape(n, heads, dim)
         k = proj[:, heads * dim: (heads + kv_heads) * dim].reshape(n, kv_heads, dim)
-        v = proj[:, (heads + kv_heads) * dim:].reshape(n, kv_heads, vdim)
+        v = k if values_from_keys else proj[:, (heads + kv_heads) * dim:].reshape(n, kv_heads, vdim)
         if q_weight is not None:
             q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight
             k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_weight
@@ -320,6 +344,10 @@ class RefOps:
             cos, sin = table[positions.long(), 0][:, None, :], table[positions.long(), 1][:, None, :]
 
             def rot(x):
+                if interleaved:
+                    x1, x2, y = x[..., 0:rot_dims:2], x[..., 1:rot_dims:2], x.clone()
+                    y[..., 0:rot_dims:2], y[..., 1:rot_dims:2] = x1 * cos - x2 * sin, x2 * cos + x1 * sin
+                    return y
                 x1, x2, rest = x[..., :half], x[..., half:rot_dims], x[..., rot_dims:]
                 return torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin, rest), dim=-1)
 
@@ -349,7 +377,7 @@ class RefOps:
             out[t] = torch.einsum("hk,khd->hd", weights, v).reshape(nh * vdim).to(out.dtype)
 
     def sink_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, vdim, page_size, scale,
-                       window, sinks, gate, out):
+                       window, sinks, gate, out, softcap=None, keep_first=0):
         groups = nh // nkv
         tables = block_tables.long().cpu()
         positions = ctx.positions.cpu().tolist()
@@ -358,10 +386,14 @@ class RefOps:
             p, s = positions[t], seqs[t]
             lo = max(0, p - window + 1) if window else 0
             keys = torch.arange(lo, p + 1)
+            if window and keep_first:
+                keys = torch.cat([torch.arange(0, min(keep_first, lo)), keys])
             pages, offs = tables[s][keys // page_size], keys % page_size
             k = k_cache[pages, :, offs].float().repeat_interleave(groups, dim=1)  # [keys, nh, hd]
             v = v_cache[pages, :, offs].float().repeat_interleave(groups, dim=1)
             scores = torch.einsum("hd,khd->hk", q[t].reshape(nh, hd).float(), k) * scale
+            if softcap:
+                scores = softcap * torch.tanh(scores / softcap)
             if sinks is not None:
                 scores = torch.cat([scores, sinks[:, None]], dim=1)
             weights = scores.softmax(-1)[:, : keys.numel()]
