@@ -1353,6 +1353,7 @@ class CudaOps:
     # requests that bring at most so many tokens have their window's keys cut among blocks, each of
     # which serves the query heads of one key/value head (tokens x heads of a group: 64 rows at most)
     SINK_SPLIT_ROWS = 8
+    SINK_SPLIT_MOST = 32  # ranges of key tiles per request where no window bounds them
 
     @_kind("attention.sink")
     def sink_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, vdim, page_size, scale,
@@ -1364,8 +1365,8 @@ class CudaOps:
         value sizes that are multiples of 16 up to 256 runs the tensor-core kernel (a block per 64
         positions of a request and head, for prompt portions and single tokens; lengths and tables
         are read on the device, and a captured step is launched for the most tokens a request can
-        bring within its bounds; when no request brings more than a few tokens and there is a
-        window, the window's key tiles are cut among blocks and merged by a second kernel, so a
+        bring within its bounds; when no request brings more than a few tokens, the key tiles of the
+        window (or, without one, of the positions the block tables hold) are cut among blocks and merged by a second kernel, so a
         decoded token's sums are the same numbers in another order than in a step that also holds
         a prompt portion); 32-bit and other sizes the general kernel, whose order of operations
         does not depend on the batch.  ``softcap``: a score ``s`` becomes ``softcap * tanh(s / softcap)``
@@ -1383,13 +1384,19 @@ class CudaOps:
             bounds = getattr(ctx, "bounds", None)
             longest = bounds[0] if bounds is not None else ctx.max_q_len  # (a captured step: its token bound)
             scratch, splits, per_split, kept_splits = None, 1, 0, 0
-            if window and longest <= self.SINK_SPLIT_ROWS and longest * (nh // nkv) <= 64:
+            if longest <= self.SINK_SPLIT_ROWS and longest * (nh // nkv) <= 64:
                 # the tiles between the first row's oldest key and the last row's own position, in
                 # ranges of two: from the window and the row bound alone, so a captured launch stays valid;
-                # the tiles of the kept first keys are ranges of their own in front of them
-                tiles = (int(window) + longest - 2) // 64 + 2
+                # the tiles of the kept first keys are ranges of their own in front of them.  Without a
+                # window: the tiles of as many positions as the step's block tables hold, in at most
+                # SINK_SPLIT_MOST ranges (a block whose range lies behind its request's end leaves at once).
                 kept_tiles = -(-keep // 64)
-                per_split = max(2, -(-(tiles + kept_tiles) // 1022))  # (the merge kernel takes up to 1,024 ranges)
+                if window:
+                    tiles = (int(window) + longest - 2) // 64 + 2
+                    per_split = max(2, -(-(tiles + kept_tiles) // 1022))  # (the merge kernel takes up to 1,024 ranges)
+                else:
+                    tiles = -(-block_tables.shape[1] * page_size // 64)
+                    per_split = max(2, -(-tiles // self.SINK_SPLIT_MOST))
                 kept_splits = -(-kept_tiles // per_split)
                 splits = -(-tiles // per_split) + kept_splits
                 if splits > 1:

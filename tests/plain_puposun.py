@@ -1,4 +1,5 @@
-"""A plain, slow Puposun in 32-bit PyTorch: whole sequences, no cache, one function per mechanism.
+"""A plain, slow Puposun in PyTorch (64-bit unless asked otherwise): whole sequences, no cache, one
+function per mechanism.
 
 The oracle of the Puposun tests.  It shares no code with the engine: it takes the configuration as
 the dictionary ``config.json`` holds and the tensors by their stored names.
@@ -16,15 +17,12 @@ are capped by ``c * tanh(logits / c)``.
 
 from __future__ import annotations
 
-import math
-
 import torch
 
 
 def rms_norm(x, weight, eps):
-    x = x.float()
     y = x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps)
-    return y if weight is None else y * weight.float()
+    return y if weight is None else y * weight
 
 
 def rotate(x, positions, dims, base, layout):
@@ -32,9 +30,9 @@ def rotate(x, positions, dims, base, layout):
     if not dims:
         return x
     half = dims // 2
-    i = torch.arange(half, dtype=torch.float32)
-    freq = torch.pow(torch.tensor(float(base), dtype=torch.float32), -2.0 * i / dims)
-    ang = positions.float()[:, None] * freq[None, :]
+    i = torch.arange(half, dtype=x.dtype)
+    freq = torch.pow(torch.tensor(float(base), dtype=x.dtype), -2.0 * i / dims)
+    ang = positions.to(x.dtype)[:, None] * freq[None, :]
     cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
     out = x.clone()
     if layout == "halves":
@@ -63,7 +61,7 @@ def attention_core(q, k, v, scale, mask, softcap=None, sink=False):
     T, H, _ = q.shape
     G = k.shape[1]
     rep = H // G
-    out = torch.zeros(T, H, v.shape[-1])
+    out = torch.zeros(T, H, v.shape[-1], dtype=q.dtype)
     for h in range(H):
         g = h // rep
         s = (q[:, h] @ k[:, g].T) * scale
@@ -84,23 +82,23 @@ def mixer_attention(w, p, h, m):
     """Rotate-half rotation, capped scores, zero sink, biases; the values are the unrotated keys."""
     T = h.shape[0]
     H, G, d = m["heads"], m["kv_heads"], m["dim"]
-    q = (h @ w[p + ".q"].float().T + w[p + ".q.b"].float()).view(T, H, d)
-    k = (h @ w[p + ".k"].float().T + w[p + ".k.b"].float()).view(T, G, d)
+    q = (h @ w[p + ".q"].T + w[p + ".q.b"]).view(T, H, d)
+    k = (h @ w[p + ".k"].T + w[p + ".k.b"]).view(T, G, d)
     v = k
     pos = torch.arange(T)
     rot = m.get("rot") or {}
     q = rotate(q, pos, rot.get("dims", 0), rot.get("base", 1.0), "halves")
     kr = rotate(k, pos, rot.get("dims", 0), rot.get("base", 1.0), "halves")
     o = attention_core(q, kr, v, m["scale"], visible(T), m.get("softcap"), sink=True)
-    return o.reshape(T, -1) @ w[p + ".o"].float().T + w[p + ".o.b"].float()
+    return o.reshape(T, -1) @ w[p + ".o"].T + w[p + ".o.b"]
 
 
 def mixer_attention_2(w, p, h, m):
     """Interleaved rotation, window with kept first tokens, a gate per head; values are the unrotated keys."""
     T = h.shape[0]
     H, G, d = m["heads"], m["kv_heads"], m["dim"]
-    q = (h @ w[p + ".q"].float().T).view(T, H, d)
-    k = (h @ w[p + ".k"].float().T).view(T, G, d)
+    q = (h @ w[p + ".q"].T).view(T, H, d)
+    k = (h @ w[p + ".k"].T).view(T, G, d)
     v = k
     pos = torch.arange(T)
     rot = m.get("rot") or {}
@@ -109,40 +107,48 @@ def mixer_attention_2(w, p, h, m):
     mask_cfg = m.get("mask") or {}
     mask = visible(T, mask_cfg.get("size"), mask_cfg.get("keep_first", 0))
     o = attention_core(q, kr, v, m["scale"], mask)
-    gate = torch.sigmoid(h @ w[p + ".g"].float().T)  # [T, H]
+    gate = torch.sigmoid(h @ w[p + ".g"].T)  # [T, H]
     o = o * gate[:, :, None]
-    return o.reshape(T, -1) @ w[p + ".o"].float().T
+    return o.reshape(T, -1) @ w[p + ".o"].T
 
 
-def route(w, p, h, mlp):
-    """(ids [T, top], weights [T, top]) of the mixture's router."""
+def route(w, p, h, mlp, margins=None):
+    """(ids [T, top], weights [T, top]) of the mixture's router.  ``margins``: a list that receives, per
+    token, how far the last chosen expert's choice score is above the best one that was not chosen,
+    and how far the last kept group's score is above the best one that was dropped."""
     r = mlp["router"]
     E, top = r["experts"], r["top"]
     groups = r.get("groups") or {"count": 1, "keep": 1}
-    s = torch.sigmoid(h @ w[p + ".router"].float().T)
-    choice = s + w[p + ".correction"].float()
+    s = torch.sigmoid(h @ w[p + ".router"].T)
+    choice = s + w[p + ".correction"]
     per = E // groups["count"]
     if groups["keep"] < groups["count"]:
         by_group = choice.view(-1, groups["count"], per)
         gscore = by_group.topk(min(2, per), dim=-1).values.sum(-1)
         kept = gscore.topk(groups["keep"], dim=-1).indices
+        if margins is not None:
+            ranked = gscore.sort(-1, descending=True).values
+            margins.extend((ranked[:, groups["keep"] - 1] - ranked[:, groups["keep"]]).tolist())
         allowed = torch.zeros_like(gscore, dtype=torch.bool).scatter_(1, kept, True)
         choice = choice.masked_fill(~allowed[:, :, None].expand(-1, -1, per).reshape(-1, E), float("-inf"))
     ids = choice.topk(top, dim=-1).indices
+    if margins is not None and top < (choice > float("-inf")).sum(-1).min():
+        ranked = choice.sort(-1, descending=True).values
+        margins.extend((ranked[:, top - 1] - ranked[:, top]).tolist())
     picked = s.gather(1, ids)
     weights = picked / (picked.sum(-1, keepdim=True) + 1e-20) * r["scale"]
     return ids, weights
 
 
-def feed_forward_moe(w, p, h, mlp):
-    ids, weights = route(w, p, h, mlp)
-    out = torch.zeros(h.shape[0], w[p + ".e0.down"].shape[0])
+def feed_forward_moe(w, p, h, mlp, margins=None):
+    ids, weights = route(w, p, h, mlp, margins)
+    out = torch.zeros(h.shape[0], w[p + ".e0.down"].shape[0], dtype=h.dtype)
     for t in range(h.shape[0]):
         for j in range(ids.shape[1]):
             e = int(ids[t, j])
-            g = h[t] @ w[f"{p}.e{e}.gate"].float().T
-            u = h[t] @ w[f"{p}.e{e}.up"].float().T
-            out[t] += weights[t, j] * ((torch.nn.functional.silu(g) * u) @ w[f"{p}.e{e}.down"].float().T)
+            g = h[t] @ w[f"{p}.e{e}.gate"].T
+            u = h[t] @ w[f"{p}.e{e}.up"].T
+            out[t] += weights[t, j] * ((torch.nn.functional.silu(g) * u) @ w[f"{p}.e{e}.down"].T)
     return out
 
 
@@ -159,10 +165,11 @@ def run_order(cfg):
     return order + [(i, False) for i in range(stop, n)]
 
 
-def forward(cfg, w, tokens, return_layers=False):
+def forward(cfg, w, tokens, dtype=torch.float64, return_layers=False, margins=None):
     """Logits [T, vocab] of a whole sequence (and the stream after every layer run)."""
     tokens = torch.as_tensor(tokens, dtype=torch.long)
-    x0 = w["embed"].float()[tokens] * float((cfg.get("embedding") or {}).get("scale", 1.0))
+    w = {k: v.to(dtype) for k, v in w.items()}
+    x0 = w["embed"][tokens] * float((cfg.get("embedding") or {}).get("scale", 1.0))
     x = x0.clone()
     eps = cfg["norm"]["eps"]
     seen = []
@@ -173,43 +180,11 @@ def forward(cfg, w, tokens, return_layers=False):
         h = rms_norm(x, w[f"l{i}.norm1"], eps)
         mix = (mixer_attention if layer["type"] == "attention" else mixer_attention_2)(w, f"l{i}.mix", h, layer["mixer"])
         if layer.get("mlp") is not None:
-            mix = mix + feed_forward_moe(w, f"l{i}.mlp", h, layer["mlp"])
+            mix = mix + feed_forward_moe(w, f"l{i}.mlp", h, layer["mlp"], margins)
         x = x + mix
         seen.append(x.clone())
-    logits = rms_norm(x, w["final.norm"], eps) @ w["head"].float().T
+    logits = rms_norm(x, w["final.norm"], eps) @ w["head"].T
     cap = cfg.get("logit_softcap")
     if cap:
         logits = cap * torch.tanh(logits / cap)
     return (logits, torch.stack(seen)) if return_layers else logits
-
-
-def random_weights(cfg, seed=0, std=None):
-    """Seeded random tensors by stored name, rounded to bfloat16 values (kept as 32-bit)."""
-    g = torch.Generator().manual_seed(seed)
-    W, V = cfg["width"], cfg["vocab"]
-
-    def mat(o, i, s=None):
-        return (torch.randn(o, i, generator=g) * (s if s is not None else (std or 1.0 / math.sqrt(i)))).bfloat16().float()
-
-    def vec(n, s=0.1, mean=0.0):
-        return (mean + torch.randn(n, generator=g) * s).bfloat16().float()
-
-    w = {"embed": mat(V, W, 0.05), "final.norm": vec(W, 0.1, 1.0), "head": mat(V, W)}
-    for i, layer in enumerate(cfg["layers"]):
-        m, p = layer["mixer"], f"l{i}"
-        w[f"{p}.norm1"] = vec(W, 0.1, 1.0)
-        H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-        w[f"{p}.mix.q"], w[f"{p}.mix.k"], w[f"{p}.mix.o"] = mat(H * d, W), mat(G * d, W), mat(W, H * dv)
-        if layer["type"] == "attention":
-            w[f"{p}.mix.q.b"], w[f"{p}.mix.k.b"], w[f"{p}.mix.o.b"] = vec(H * d), vec(G * d), vec(W)
-        else:
-            w[f"{p}.mix.g"] = mat(H, W)
-        mlp = layer.get("mlp")
-        if mlp is not None:
-            E, ff = mlp["router"]["experts"], mlp["expert"]["ff"]
-            w[f"{p}.mlp.router"] = mat(E, W)
-            w[f"{p}.mlp.correction"] = vec(E, 0.2)
-            for e in range(E):
-                w[f"{p}.mlp.e{e}.gate"], w[f"{p}.mlp.e{e}.up"] = mat(ff, W), mat(ff, W)
-                w[f"{p}.mlp.e{e}.down"] = mat(W, ff)
-    return w
