@@ -637,6 +637,78 @@ def vofanex_rows(size: str, kinds: dict, peaks: dict, tokens: int, batch: int, c
     return rows
 
 
+# --- the Puposun design beside the closest models ------------------------------------------------
+
+PUPOSUN_SIZES = {
+    # width, (attention: heads, kv_heads, dim, rotated dims, cap of the scores),
+    # (attention_2: heads, kv_heads, dim, rotated dims, window, kept first positions),
+    # (experts: ff, count, top, groups, kept groups)
+    "w1024": (1024, (16, 4, 64, 64, 20.0), (16, 4, 64, 32, 512, 4), (512, 16, 4, 4, 2)),
+    "w2048": (2048, (16, 4, 128, 128, 20.0), (16, 4, 128, 64, 1024, 4), (1024, 32, 4, 4, 2)),
+}
+
+
+def puposun_config(size: str) -> dict:
+    """Three layers, four layer runs: attention, attention_2 twice in a row (a loop of two passes, the
+    embedding's output added again before the second), attention; every layer with experts."""
+    width, a1, a2, ex = PUPOSUN_SIZES[size]
+    full = {"heads": a1[0], "kv_heads": a1[1], "dim": a1[2], "vdim": a1[2], "scale": a1[2] ** -0.5,
+            "rot": {"dims": a1[3], "base": 500000.0}, "softcap": a1[4]}
+    windowed = {"heads": a2[0], "kv_heads": a2[1], "dim": a2[2], "vdim": a2[2], "scale": a2[2] ** -0.5,
+                "rot": {"dims": a2[3], "base": 1000000.0}, "mask": {"size": a2[4], "keep_first": a2[5]}}
+    moe = {"kind": "moe", "expert": {"ff": ex[0]},
+           "router": {"experts": ex[1], "top": ex[2], "scale": 2.5, "groups": {"count": ex[3], "keep": ex[4]}}}
+    layers = [("attention", full, moe), ("attention_2", windowed, moe), ("attention", full, moe)]
+    return {"architecture": "Puposun", "vocab": DESIGN_VOCAB, "width": width, "max_positions": MAX_CONTEXT,
+            "norm": {"eps": 1e-6}, "embedding": {"scale": 2.0}, "logit_softcap": 30.0,
+            "loop": {"start": 1, "stop": 2, "times": 2},
+            "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in layers]}
+
+
+def puposun_rows(size: str, kinds: dict, peaks: dict, tokens: int, batch: int, ctx: float, decode: bool) -> dict:
+    """Per kind of kernel of the Puposun model: microseconds per launch and, where the kind has such a
+    figure, what it is of the measured peak: decode launches against the copy rate for the bytes they
+    must read (weights, the cached rows a query sees), prompt launches against the burst bf16 rate for
+    their flops.  The attention's four launches per step are two over every earlier position and two
+    over a window: the figure is for their average."""
+    width, a1, a2, ex = PUPOSUN_SIZES[size]
+    H, G, d = a1[0], a1[1], a1[2]
+    window, kept = a2[4], a2[5]
+    eff, experts, top = ex[0], ex[1], ex[2]
+    used = min(experts, batch * top if decode else experts)
+    # (both mixers have the same heads and sizes here: the input product of attention_2 carries its head gates)
+    weights = {
+        "linear:sinkattn.in": width * ((H + G) * d + H / 2), "linear:sinkattn.delta": width * H * d,
+        "linear:head": width * DESIGN_VOCAB,
+        "routed.gate_up": 2 * eff * width * used, "routed.down": eff * width * used,
+    }
+    seen = min(window, tokens)
+    flops = {
+        "attention.sink": 2.0 * H * 2 * d * 0.5 * (tokens * tokens / 2.0 + tokens * (seen - seen * seen / (2.0 * tokens))),
+        "routed.gate_up": 2.0 * tokens * top * 2 * eff * width, "routed.down": 2.0 * tokens * top * eff * width,
+    }
+    rows = {}
+    for kind, r in kinds.items():
+        us = r["ms"] / r["launches"] * 1e3
+        out = {"us": round(us, 2), "launches": r["launches"]}
+        if decode:
+            nbytes = None
+            if weights.get(kind):
+                nbytes = 2 * weights[kind]
+            elif kind == "attention.sink":
+                nbytes = batch * 0.5 * (ctx + min(ctx, window + kept)) * G * 2 * d * 2
+            if nbytes:
+                out.update(gbs=round(nbytes / (us * 1e-6) / 1e9, 1),
+                           frac=round(nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 4))
+        else:
+            f = flops.get(kind) or (2.0 * tokens * weights[kind] if weights.get(kind) and kind != "linear:head" else None)
+            if f:
+                out.update(tflops=round(f / (us * 1e-6) / 1e12, 1),
+                           frac=round(f / (us * 1e-6) / 1e12 / peaks["bf16_tflops"], 4))
+        rows[kind] = out
+    return rows
+
+
 def run_design(args) -> dict:
     """`--design rugedra`: prompt and decode throughput of the Rugedra design at layer sizes of a real
     model's (four layers: latent attention + dense, delta rule + experts, latent attention + experts,
@@ -646,7 +718,9 @@ def run_design(args) -> dict:
     feed-forward; the middle two as a loop of one pass) beside the Rugedra and the Llama model.
     `--design vofanex`: the Vofanex design (four layers: gated linear attention + dense, windowed sink
     attention + experts, windowed sink attention + dense, gated linear attention + experts) beside
-    the Ravapel and the Llama model."""
+    the Ravapel and the Llama model.  `--design puposun`: the Puposun design (attention over every
+    earlier position, windowed attention twice in a loop, attention again; every layer with experts
+    beside its mixer) beside the Vofanex and the Llama model."""
     import torch
 
     from inference_engine_b200.engine.llm_engine import LLMEngine
@@ -667,6 +741,9 @@ def run_design(args) -> dict:
         elif args.design == "vofanex":
             models = [("vofanex", vofanex_config(size)), ("ravapel", ravapel_config(size)),
                       ("llama", llama_config_like(size))]
+        elif args.design == "puposun":
+            models = [("puposun", puposun_config(size)), ("vofanex", vofanex_config(size)),
+                      ("llama", llama_config_like(size))]
         for name, cfg in models:
             engine = LLMEngine.from_random(
                 cfg, seed=0, dtype="bfloat16", device="cuda", max_model_len=MAX_CONTEXT,
@@ -679,7 +756,10 @@ def run_design(args) -> dict:
                    "prefill_tokens_per_s": round(PREFILL_LEN / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
                    # (the prompt step is launched eagerly: what its kernels take by themselves, without the host)
                    "prefill_kernels_ms": round(sum(r["ms"] for r in kinds_prefill.values()), 3)}
-            if name == "vofanex":
+            if name == "puposun":
+                row["kernels"] = {f"decode_b{batch}": puposun_rows(size, kinds, peaks, batch, batch, ctx, True),
+                                  f"prefill_{PREFILL_LEN}": puposun_rows(size, kinds_prefill, peaks, PREFILL_LEN, 1, PREFILL_LEN, False)}
+            elif name == "vofanex":
                 row["kernels"] = {f"decode_b{batch}": vofanex_rows(size, kinds, peaks, batch, batch, ctx, True),
                                   f"prefill_{PREFILL_LEN}": vofanex_rows(size, kinds_prefill, peaks, PREFILL_LEN, 1, PREFILL_LEN, False)}
             elif name == "ravapel":
@@ -816,7 +896,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--design", default=None, choices=["rugedra", "ravapel", "vofanex"],
+    ap.add_argument("--design", default=None, choices=["rugedra", "ravapel", "vofanex", "puposun"],
                     help="instead of the default workload: this design at real layer sizes beside the closest "
                          "model the engine had, prompt and decode throughput and every kind of kernel")
     ap.add_argument("--sizes", default="w1024,w2048", help="with --design: which of " + ",".join(DESIGN_SIZES))

@@ -77,7 +77,9 @@ class RoutedExperts(FeedForward):
         if self.router_bias_name is not None:
             out[self.router_bias_name] = WeightDecl((self.experts,), "vector")
         if self.correction_name is not None:
-            out[self.correction_name] = WeightDecl((self.experts,), "vector")
+            # (drawn as zeros in the random-weights mode: a random correction, the same for every token,
+            # would send all tokens to the same few experts)
+            out[self.correction_name] = WeightDecl((self.experts,), "vector", "zeros")
         for e in range(self.experts):
             out[self._name(e, "gate")] = WeightDecl((i, h))
             out[self._name(e, "up")] = WeightDecl((i, h))

@@ -121,3 +121,36 @@ def test_generate_runs_a_vofanex_folder(tmp_path, capsys):
     for _ in range(6):
         ids.append(int(P.forward(cfg, weights, ids, torch.float64)[-1].argmax()))
     assert capsys.readouterr().out.split() == [str(t) for t in ids[len(prompt):]]
+
+
+def test_info_prints_a_puposun_shape(tmp_path, capsys):
+    from tests import puposun_configs as V
+
+    folder = H.write_model_dir(tmp_path / "m", V.MIXED, V.make_weights(V.MIXED, seed=2))
+    assert cli.main(["info", "--model", str(folder), "--gpu-mem", "180"]) == 0
+    out = capsys.readouterr().out
+    assert "architecture        Puposun" in out and "layers / width      4 / 72" in out
+    assert "attention+moe, attention_2+moe, attention_2, attention+moe" in out
+    assert "loop                layers 1..2 x 2" in out and "attention windows   7 (+ first 0), 10 (+ first 3)" in out
+
+
+@pytest.mark.gpu
+def test_generate_runs_a_puposun_folder(tmp_path, capsys):
+    """`engine generate` on a Puposun folder: the same entry point, scheduler and sampling as for the
+    other architectures; greedy tokens are the plain implementation's."""
+    import torch
+
+    from tests import plain_puposun as P
+    from tests import puposun_configs as V
+
+    cfg, weights = V.MIXED, V.make_weights(V.MIXED, seed=2)
+    folder = H.write_model_dir(tmp_path / "m", cfg, weights)
+    prompt = [5, 17, 3, 44, 9, 21, 30, 8, 100, 61, 2, 77, 13]
+    rc = cli.main(["generate", "--model", str(folder), "--prompt-ids", ",".join(map(str, prompt)), "--temperature", "0",
+                   "--max-tokens", "6", "--dtype", "float32", "--num-blocks", "16", "--block-size", "8",
+                   "--max-num-seqs", "2", "--max-num-batched-tokens", "4"])
+    assert rc == 0
+    ids = list(prompt)
+    for _ in range(6):
+        ids.append(int(P.forward(cfg, weights, ids, torch.float64)[-1].argmax()))
+    assert capsys.readouterr().out.split() == [str(t) for t in ids[len(prompt):]]

@@ -753,14 +753,3 @@ def test_captured_short_steps_with_portions(tmp_path, dtype):
             for rid in requests:
                 assert torch.equal(results[(True, mode)][rid], results[(False, mode)][rid]), (mode, rid)
     get_ops("cuda").check_errors()
-
-
-def test_replay_program_describes_the_model(tmp_path, capsys):
-    """`engine info` reads a Puposun folder through the architecture registry."""
-    from inference_engine_b200.config import load_config
-    from inference_engine_b200.config.registry import get_architecture
-
-    folder = H.write_model_dir(tmp_path / "m", V.MIXED, V.make_weights(V.MIXED, seed=1))
-    cfg = load_config(folder)
-    lines = get_architecture(cfg.architecture).describe(cfg)
-    assert any("layers 1..2 x 2" in line for line in lines) and any("10 (+ first 3)" in line for line in lines)
