@@ -643,8 +643,8 @@ PUPOSUN_SIZES = {
     # width, (attention: heads, kv_heads, dim, rotated dims, cap of the scores),
     # (attention_2: heads, kv_heads, dim, rotated dims, window, kept first positions),
     # (experts: ff, count, top, groups, kept groups)
-    "w1024": (1024, (16, 4, 64, 64, 20.0), (16, 4, 64, 32, 512, 4), (512, 16, 4, 4, 2)),
-    "w2048": (2048, (16, 4, 128, 128, 20.0), (16, 4, 128, 64, 1024, 4), (1024, 32, 4, 4, 2)),
+    "w1024": (1024, (16, 4, 64, 64, 40.0), (16, 4, 64, 32, 512, 4), (512, 16, 4, 4, 2)),
+    "w2048": (2048, (16, 4, 128, 128, 40.0), (16, 4, 128, 64, 1024, 4), (1024, 32, 4, 4, 2)),
 }
 
 
@@ -653,14 +653,14 @@ def puposun_config(size: str) -> dict:
     embedding's output added again before the second), attention; every layer with experts."""
     width, a1, a2, ex = PUPOSUN_SIZES[size]
     full = {"heads": a1[0], "kv_heads": a1[1], "dim": a1[2], "vdim": a1[2], "scale": a1[2] ** -0.5,
-            "rot": {"dims": a1[3], "base": 500000.0}, "softcap": a1[4]}
+            "rot": {"dims": a1[3], "base": 10000.0}, "softcap": a1[4]}
     windowed = {"heads": a2[0], "kv_heads": a2[1], "dim": a2[2], "vdim": a2[2], "scale": a2[2] ** -0.5,
-                "rot": {"dims": a2[3], "base": 1000000.0}, "mask": {"size": a2[4], "keep_first": a2[5]}}
+                "rot": {"dims": a2[3], "base": 10000.0}, "mask": {"size": a2[4], "keep_first": a2[5]}}
     moe = {"kind": "moe", "expert": {"ff": ex[0]},
-           "router": {"experts": ex[1], "top": ex[2], "scale": 2.5, "groups": {"count": ex[3], "keep": ex[4]}}}
+           "router": {"experts": ex[1], "top": ex[2], "scale": 2.0, "groups": {"count": ex[3], "keep": ex[4]}}}
     layers = [("attention", full, moe), ("attention_2", windowed, moe), ("attention", full, moe)]
     return {"architecture": "Puposun", "vocab": DESIGN_VOCAB, "width": width, "max_positions": MAX_CONTEXT,
-            "norm": {"eps": 1e-6}, "embedding": {"scale": 2.0}, "logit_softcap": 30.0,
+            "norm": {"eps": 1e-6}, "embedding": {"scale": 2.0}, "logit_softcap": 50.0,
             "loop": {"start": 1, "stop": 2, "times": 2},
             "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in layers]}
 

@@ -16,11 +16,11 @@ experts of ``expert.ff`` units, ``router.top`` per token, ``router.groups.count`
 The model: token embedding times a constant.  A layer: ``x <- x + mixer(h) + feed_forward(h)`` with
 ``h = rms(x) * norm1``.  Both mixers are grouped-query softmax attention with ``v = k`` as projected,
 before the rotation.  ``attention``: rotation of pairs ``(i, i + dims / 2)``, biases on queries, keys
-and the output, scores capped by ``softcap * tanh(s / softcap)``, every earlier position visible, one
-added to the softmax's denominator (a sink of score 0).  ``attention_2``: rotation of pairs
+and the output, scores capped by ``softcap * tanh(s / softcap)``, every earlier position visible, and a
+term ``exp(0)`` in the softmax's denominator that has neither key nor value (a sink).  ``attention_2``: rotation of pairs
 ``(2i, 2i + 1)``, no biases, a sliding window that also keeps the first ``keep_first`` positions
 visible, a sigmoid gate per head.  The router scores experts by the sigmoid of its logits, chooses
-by score plus a stored correction within the groups whose two best choice scores add up highest, and
+by score plus a stored correction, within the groups whose two best such values add up highest, and
 weighs the chosen by their plain scores over their sum, times a constant.  Layers ``loop.start ..
 loop.stop - 1`` run ``loop.times`` times in a row with the same weights and a cache of their own per
 pass; before each pass but the first the embedding's output is added to the stream.  The logits are

@@ -6,7 +6,7 @@
 //    and their scores divided by their sum (+ 1e-20), times `weight_scale`.  With `sigmoid_scores` an
 //    expert's score is the sigmoid of its logit instead; a `correction` per expert is then added for
 //    the choice alone (groups and experts are chosen by score + correction, the weights are the plain
-//    scores), a group's score is the sum of its `group_top` (1 or 2) largest choice scores, and the
+//    scores), a group is ranked by its best `group_top` (1 or 2) corrected scores added up, and the
 //    experts of groups that are not kept cannot be chosen whatever their sign.
 //  * routed_align: the step's (token, choice) pairs sorted by expert into tiles of TILE_M rows:
 //    every expert's run of pairs is padded to whole tiles (padding rows are -1), and a list says
@@ -91,7 +91,7 @@ route_topk_kernel(const T* __restrict__ x, const float* __restrict__ w, const fl
         __syncwarp();
         int per = experts / groups;
         if (keep < groups) {
-            for (int g = lane; g < groups; g += 32) {  // the group's largest choice scores, one or two of them
+            for (int g = lane; g < groups; g += 32) {  // the group's best corrected scores, one or two of them
                 float b1 = -INFINITY, b2 = -INFINITY;
                 for (int e = g * per; e < (g + 1) * per; ++e) {
                     float c = choice[e];

@@ -1049,8 +1049,8 @@ class CudaOps:
         """Softmax scores (of the router's logits plus ``bias``, if given), group limit and the ``top``
         experts per token with their normalised weights, times ``weight_scale``.  ``scoring="sigmoid"``:
         the scores are the logits' sigmoids; ``correction`` (one number per expert) is added to them
-        for the choice of groups and experts only, and a group's score is the sum of its
-        ``group_top`` (1 or 2) largest choice scores."""
+        for the choice of groups and experts only, and a group is ranked by its best ``group_top``
+        (1 or 2) corrected scores added up."""
         if scoring not in ("softmax", "sigmoid"):
             raise KernelError(f"route_topk: no scoring {scoring!r}")
         if correction is not None and (correction.dtype != self.torch.float32 or correction.numel() != w_router.shape[0]):

@@ -7,8 +7,8 @@ router has one: ``router_bias``), in 32-bit.  The experts form
 ``top`` allowed experts with the largest scores are taken, and their scores, divided by their sum
 (+ 1e-20), weigh the experts' outputs (without groups this is the softmax over the chosen logits).
 ``scoring="sigmoid"``: a score is the sigmoid of the expert's logit; a ``correction`` per expert (a
-tensor, if named) is added to the scores for the choice of groups and experts alone, a group's score
-is the sum of its ``group_top`` largest choice scores, and the weights are the chosen experts' plain
+tensor, if named) is added to the scores for the choice of groups and experts alone, a group is ranked
+by its best ``group_top`` corrected scores added up, and the weights are the chosen experts' plain
 scores over their sum.  ``weight_scale`` multiplies the weights.
 
 An expert: ``g = min(gate(x), limit)``, ``u = clamp(up(x), -limit, limit)``,

@@ -15,7 +15,7 @@ Variants by parameters.  ``values="keys"``: there is no value projection; the va
 projected (with their bias), before the rotation, so the cache holds a rotated and a plain copy of
 each key row, and only queries and keys may have biases.  ``softcap``: a score ``s`` becomes
 ``softcap * tanh(s / softcap)`` before the softmax.  ``sink_value``: the sink is this constant for
-every head instead of a learned tensor (0: one is added to the softmax's denominator).
+every head instead of a learned tensor (0: the denominator's extra term is ``exp(0)``).
 ``keep_first`` (with a window): the first positions of a request stay visible to all its later
 queries, at their own positions, and their pages are kept.  A rotary encoding of either layout
 (halves or interleaved pairs) on the first ``rotary_dim`` entries of each head.  ``o_bias`` among

@@ -114,7 +114,7 @@ def mixer_attention_2(w, p, h, m):
 
 def route(w, p, h, mlp, margins=None):
     """(ids [T, top], weights [T, top]) of the mixture's router.  ``margins``: a list that receives, per
-    token, how far the last chosen expert's choice score is above the best one that was not chosen,
+    token, how far the last chosen expert's corrected score is above the best one that was not chosen,
     and how far the last kept group's score is above the best one that was dropped."""
     r = mlp["router"]
     E, top = r["experts"], r["top"]

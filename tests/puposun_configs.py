@@ -67,10 +67,10 @@ ODD = config(50, 61, [
 # the loop starts at the first layer and runs three times; a window of one position beside two kept
 # ones; a window wider than any prompt; an embedding scale of one
 LOOP_FIRST = config(64, 97, [
-    (attention(4, 2, 16, rot=16, softcap=8.0), moe(4, 2, 20, groups=2, keep=1, scale=2.5)),
+    (attention(4, 2, 16, rot=16, softcap=8.0), moe(4, 2, 20, groups=2, keep=1, scale=2.2)),
     (attention_2(4, 4, 16, rot=2, window=1, keep_first=2), moe(3, 1, 12)),
     (attention_2(2, 2, 8, rot=8, window=500, keep_first=4), None),
-], scale=1.0, loop=(0, 2, 3), logit_softcap=30.0)
+], scale=1.0, loop=(0, 2, 3), logit_softcap=25.0)
 # the loop ends with the last layer and runs once (nothing is added again)
 LOOP_LAST = config(48, 83, [
     (attention_2(2, 1, 24, rot=12, window=9, keep_first=1), moe(6, 2, 10, groups=3, keep=2)),
@@ -81,8 +81,8 @@ LOOP_LAST = config(48, 83, [
 WIDE = config(128, 211, [
     (attention(8, 2, 64, rot=32, softcap=15.0), moe(8, 2, 64, groups=4, keep=2, scale=2.0)),
     (attention_2(4, 4, 32, rot=32, window=100, keep_first=5), moe(8, 3, 32, groups=2, keep=1)),
-    (attention_2(6, 3, 128, rot=64, base=1e6, window=257, keep_first=70), None),
-    (attention(4, 1, 48, rot=48, base=5e5, softcap=30.0), moe(4, 1, 48)),
+    (attention_2(6, 3, 128, rot=64, base=2e5, window=257, keep_first=70), None),
+    (attention(4, 1, 48, rot=48, base=3e4, softcap=30.0), moe(4, 1, 48)),
 ], scale=2.0, loop=(1, 3, 2), logit_softcap=20.0)
 
 CONFIGS = {"mixed": MIXED, "odd": ODD, "loop_first": LOOP_FIRST, "loop_last": LOOP_LAST}
